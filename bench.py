@@ -44,6 +44,8 @@ def parse():
     ap.add_argument("--model", default="llama-3-8b")
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--prompt-len", type=int, default=1024)
+    ap.add_argument("--out-len", type=int, default=256,
+                    help="output tokens per request of the workload: the timed steps sit around its middle")
     ap.add_argument("--layers", type=int, default=0, help="debug only: override layer count (invalidates the number)")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--parallel", default="tp", choices=["tp", "ep", "dp_ep"],
@@ -140,7 +142,10 @@ def main():
     K, W, P = args.steps, max(args.warmup, 3), args.prompt_len
     B_global = args.batch
     B = B_global // ctx.dp          # requests this rank schedules
-    total_new = W + K + 8
+    # the timed end-to-end window is centred on the middle of the configured decode (context
+    # prompt + out_len / 2); `advance` untimed steps bring the batch there after the warm-up
+    advance = max(0, args.out_len // 2 - K // 2 - W)
+    total_new = W + advance + K + 8
     overrides = dict(tp_size=ctx.tp, dp_size=ctx.dp, ep_size=ctx.ep, max_batch_size=B,
                      max_seq_len=P + 2 * total_new + 64, max_num_batched_tokens=args.max_tokens)
     if args.layers:
@@ -153,7 +158,7 @@ def main():
 
     if args.impl == "torch":
         from gvirt_b200.utils.torch_floor import run_floor
-        res = run_floor(cfg, ctx, B, P, K, W)
+        res = run_floor(cfg, ctx, B, P, K, W, advance)
         if rank == 0:
             print(json.dumps(res))
         return 0
@@ -182,7 +187,7 @@ def main():
     torch.cuda.synchronize()
     prefill_s = time.perf_counter() - t0
     ttfts = sorted(r.first_token_time - r.arrival for r in reqs)
-    for _ in range(W):
+    for _ in range(W + advance):
         llm.step()
     torch.cuda.synchronize()
 
@@ -198,12 +203,17 @@ def main():
     if rank == 0:
         sampler.start()
     n_before = [len(r.token_times) for r in reqs]
+    step_ends = []
     t0 = time.perf_counter()
     for _ in range(K):
         llm.step()
+        step_ends.append(time.perf_counter())
     barrier()
     e2e_s = time.perf_counter() - t0
     n_after = [len(r.token_times) for r in reqs]
+    # host-side time of every step after the first (with asynchronous scheduling a step returns
+    # when the previous step's tokens are in, so the differences are steady-state step times)
+    step_ms = sorted((b - a) * 1e3 for a, b in zip(step_ends, step_ends[1:]))
     h2d = (runner.h2d_bytes - h2d0) / K
     d2h = (runner.d2h_bytes - d2h0) / K
     launches_e2e = runner.launch_count - l0
@@ -240,10 +250,12 @@ def main():
 
     # time per output token inside the timed end-to-end window (one-off costs such as the first
     # capture of a decode graph and the wait behind other requests' prefill chunks are in TTFT)
+    # only gaps between tokens that both arrived inside the window count: the barrier and the
+    # start of the clock sampler in front of it are not part of any gap
     tpots = []
     for r, a, b in zip(reqs, n_before, n_after):
-        if b - a >= 1 and a >= 1:
-            tpots.append((r.token_times[b - 1] - r.token_times[a - 1]) / (b - a))
+        if b - a >= 2:
+            tpots.append((r.token_times[b - 1] - r.token_times[a]) / (b - a - 1))
     # max over ranks
     t = torch.tensor([dev_ms, e2e_s * 1e3], dtype=torch.float64, device="cuda")
     if world > 1:
@@ -257,19 +269,22 @@ def main():
             "steps": K, "warmup": W, "ms_per_step": round(dev_ms / K, 4), "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
             "config": {"model": cfg.name, "global_batch": B_global, "seq_len": P,
-                       "decode_context": P + W + K,
+                       "out_len": args.out_len, "decode_context": P + W + advance + K,
+                       "e2e_context": [P + W + advance, P + W + advance + K],
                        "parallelism": {"tp": f"tp{world}", "ep": f"tp{world}_ep{world}",
                                        "dp_ep": f"dp{world}_ep{world}"}[par],
                        "quant": cfg.quant or "none", "router_zipf": args.router_zipf or None, "layers": cfg.num_layers, "kv_block": cfg.block_size,
                        "l2_policy": "inputs larger than L2 (weights + KV streamed from HBM every step)",
                        "cuda_graph": not args.no_graph},
             "e2e": {"value": round(e2e_value, 1), "unit": "tok/s", "ms_per_step": round(e2e_ms / K, 4),
-                    "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
+                    "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+                    "step_ms_p50": round(statistics.median(step_ms), 4) if step_ms else None,
+                    "step_ms_max": round(step_ms[-1], 4) if step_ms else None},
             "gpu_launches": int(launches),
             "clocks": clocks,
             "ttft_p50_s": round(statistics.median(ttfts), 4) if ttfts else None,
             "tpot_p50_s": round(statistics.median(tpots), 5) if tpots else None,
-            "tpot_window": "the timed end-to-end steps (batch in steady decode)",
+            "tpot_window": "gaps between tokens inside the timed end-to-end steps (batch in steady decode)",
             "prefill_tok_s": round(B_global * P / prefill_s, 1),
             "status_word": status, "build_s": round(build_s, 1),
         }

@@ -19,7 +19,8 @@
 namespace gv {
 
 constexpr int DEC_WARPS = 4;
-// Tile shape of the variant the regular and the allocation-free entry points use by default.
+// Tile shape of the allocation-free entry point (the regular entry point picks a variant, by
+// default 16 tokens x 3 stages: see g_decode_variant).
 constexpr int DEC_TOK = 32;     // kv tokens per warp tile
 constexpr int DEC_STAGES = 2;
 
@@ -74,7 +75,9 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc,
     const int pos = start + tile * DEC_TOK + lane;  // this lane resolves row `lane`
     long long slot = -1;
     if (pos < end) {
-      const int blk = bt[pos / block_size];
+      // a sequence length beyond the block-table row is bad metadata: flag it, read nothing
+      const int bi = pos / block_size;
+      const int blk = bi < max_blocks ? bt[bi] : -1;
       if (blk < 0 || blk >= num_blocks) atomicOr(status, GV_ST_BAD_INDEX);
       else slot = (long long)blk * block_size + pos % block_size;
     }
@@ -364,7 +367,6 @@ static __device__ __align__(256) unsigned int g_noalloc_status[64];
 struct NoAllocDevice {
   void* scratch = nullptr;        // device address of g_noalloc_scratch on this device
   unsigned int* status = nullptr; // device address of g_noalloc_status on this device
-  bool smem_set[2] = {false, false};
 };
 static NoAllocDevice g_noalloc_dev[64];
 static std::mutex g_noalloc_mu;
@@ -394,6 +396,19 @@ static int noalloc_setup(NoAllocDevice** out) {
       set_last_error("noalloc: cudaGetSymbolAddress(status)", e);
       return GV_ECUDA;
     }
+    // opt in to the kernels' dynamic shared memory here, under the same lock, so that two host
+    // threads making their first calls at once cannot interleave the set-up
+    e = cudaFuncSetAttribute(paged_decode_kernel<64, DEC_TOK, DEC_STAGES>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             DEC_WARPS * DEC_STAGES * 2 * DEC_TOK * 64 * 2);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(paged_decode_kernel<128, DEC_TOK, DEC_STAGES>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               DEC_WARPS * DEC_STAGES * 2 * DEC_TOK * 128 * 2);
+    if (e != cudaSuccess) {
+      set_last_error("noalloc paged_decode: smem attr", e);
+      return GV_ECUDA;
+    }
     d.status = static_cast<unsigned int*>(s);
     d.scratch = p;
   }
@@ -402,20 +417,12 @@ static int noalloc_setup(NoAllocDevice** out) {
 }
 
 template <int HD>
-static int launch_decode_noalloc(NoAllocDevice* d, int slot, const void* q, const void* kc,
+static int launch_decode_noalloc(NoAllocDevice* d, const void* q, const void* kc,
                                  const void* vc, const void* bt, const void* lens, void* out,
                                  int batch, int nq, int nkv, int block_size, int max_blocks,
                                  int nsplit, float scale, long long num_blocks, cudaStream_t st) {
   constexpr int SMEM = DEC_WARPS * DEC_STAGES * 2 * DEC_TOK * HD * 2;
   auto kern = paged_decode_kernel<HD, DEC_TOK, DEC_STAGES>;
-  if (!d->smem_set[slot]) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-    if (e != cudaSuccess) {
-      set_last_error("noalloc paged_decode: smem attr", e);
-      return GV_ECUDA;
-    }
-    d->smem_set[slot] = true;
-  }
   // scratch layout: part_o [batch*nq*nsplit*HD] fp32, then part_lse [batch*nq*nsplit] fp32
   float* part_o = static_cast<float*>(d->scratch);
   float* part_lse = part_o + (size_t)batch * nq * nsplit * HD;
@@ -466,10 +473,10 @@ extern "C" int gv_paged_attention_decode_noalloc(const void* q, const void* k_ca
   if (rc != GV_OK) return rc;
   cudaStream_t st = (cudaStream_t)stream;
   if (head_dim == 64)
-    return launch_decode_noalloc<64>(d, 0, q, k_cache, v_cache, block_tables, seq_lens, out,
+    return launch_decode_noalloc<64>(d, q, k_cache, v_cache, block_tables, seq_lens, out,
                                      (int)batch, (int)nq, (int)nkv, (int)block_size,
                                      (int)max_blocks, (int)nsplit, scale, num_blocks, st);
-  return launch_decode_noalloc<128>(d, 1, q, k_cache, v_cache, block_tables, seq_lens, out,
+  return launch_decode_noalloc<128>(d, q, k_cache, v_cache, block_tables, seq_lens, out,
                                     (int)batch, (int)nq, (int)nkv, (int)block_size,
                                     (int)max_blocks, (int)nsplit, scale, num_blocks, st);
 }
@@ -484,6 +491,18 @@ extern "C" int gv_noalloc_status_read(unsigned int* host_out, void* stream) {
   if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
   if (e != cudaSuccess) {
     set_last_error("gv_noalloc_status_read", e);
+    return GV_ECUDA;
+  }
+  return GV_OK;
+}
+
+extern "C" int gv_noalloc_status_reset(void* stream) {
+  NoAllocDevice* d = nullptr;
+  int rc = noalloc_setup(&d);
+  if (rc != GV_OK) return rc;
+  cudaError_t e = cudaMemsetAsync(d->status, 0, sizeof(unsigned int), (cudaStream_t)stream);
+  if (e != cudaSuccess) {
+    set_last_error("gv_noalloc_status_reset", e);
     return GV_ECUDA;
   }
   return GV_OK;

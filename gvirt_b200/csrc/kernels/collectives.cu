@@ -82,7 +82,7 @@ __device__ __forceinline__ void exchange_flags(const CollArgs& a, int bank, unsi
   if ((int)threadIdx.x < a.R) {
     __threadfence_system();
     st_release_sys(flag_ptr(a, threadIdx.x, bank, blockIdx.x, a.rank), gen);
-    if (!wait_ge_sys(flag_ptr(a, a.rank, bank, blockIdx.x, threadIdx.x), gen))
+    if (!wait_ge_sys(flag_ptr(a, a.rank, bank, blockIdx.x, threadIdx.x), gen, peer_budget(a.status)))
       atomicOr(a.status, GV_ST_TIMEOUT_PEER);
   }
   __syncthreads();
@@ -219,13 +219,14 @@ __device__ __forceinline__ uint4 ld_line(const uint4* p) {
                : "memory");
   return v;
 }
-__device__ __forceinline__ bool wait_line(const uint4* p, uint32_t gen, uint4& v) {
+__device__ __forceinline__ bool wait_line(const uint4* p, uint32_t gen, uint4& v,
+                                          unsigned long long budget_ns = GV_WAIT_NS) {
   if (v.y == gen && v.w == gen) return true;
   const unsigned long long t0 = global_ns();
   for (unsigned int i = 0; i < GV_SPIN_LIMIT; ++i) {
     v = ld_line(p);
     if (v.y == gen && v.w == gen) return true;
-    if ((i & 63u) == 63u && global_ns() - t0 > GV_WAIT_NS) return false;
+    if ((i & 63u) == 63u && global_ns() - t0 > budget_ns) return false;
   }
   return false;
 }
@@ -297,7 +298,7 @@ collective_ll_kernel(int mode, const uint2* __restrict__ x, uint2* __restrict__ 
         if (s == a.rank) {
           acc_line<T>(acc, own.x, own.y);
         } else {
-          if (!wait_line(base + (long long)s * l_cap + l, gen, v[s])) ok = false;
+          if (!wait_line(base + (long long)s * l_cap + l, gen, v[s], ok ? peer_budget(a.status) : 0ull)) ok = false;
           acc_line<T>(acc, v[s].x, v[s].z);
         }
       }
@@ -314,7 +315,7 @@ collective_ll_kernel(int mode, const uint2* __restrict__ x, uint2* __restrict__ 
     for (long long l = gtid; l < L; l += gstride) {
       if ((int)((l >> 5) % a.R) == a.rank) continue;
       uint4 v = ld_line(base + (long long)a.R * l_cap + l);
-      if (!wait_line(base + (long long)a.R * l_cap + l, gen, v)) ok = false;
+      if (!wait_line(base + (long long)a.R * l_cap + l, gen, v, ok ? peer_budget(a.status) : 0ull)) ok = false;
       out[l] = make_uint2(v.x, v.z);
     }
     if (!ok) atomicOr(a.status, GV_ST_TIMEOUT_PEER);
@@ -349,7 +350,7 @@ collective_ll_kernel(int mode, const uint2* __restrict__ x, uint2* __restrict__ 
       if (s == a.rank) {
         d = own;
       } else {
-        if (!wait_line(base + (long long)s * l_cap + l, gen, v[s])) ok = false;
+        if (!wait_line(base + (long long)s * l_cap + l, gen, v[s], ok ? peer_budget(a.status) : 0ull)) ok = false;
         d = make_uint2(v[s].x, v[s].z);
       }
       if (mode == 5) out[(long long)s * L + l] = d;

@@ -186,6 +186,14 @@ __device__ __forceinline__ bool wait_ge_sys(const unsigned int* p, unsigned int 
   return false;
 }
 
+// Time budget of a wait on a peer: all of GV_WAIT_NS, or 1 ms once a peer wait on this device has
+// already run out (the time-out bit of the status word is up). A peer that is gone then costs one
+// full wait per launch, not one per remaining line, tile or flag bank.
+__device__ __forceinline__ unsigned long long peer_budget(const unsigned int* status) {
+  return (*reinterpret_cast<const volatile unsigned int*>(status) & GV_ST_TIMEOUT_PEER) ? 1000000ull
+                                                                                        : GV_WAIT_NS;
+}
+
 #endif  // __CUDACC__
 
 }  // namespace gv

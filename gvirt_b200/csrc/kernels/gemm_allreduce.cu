@@ -68,13 +68,14 @@ __device__ __forceinline__ uint4 ld_line(const uint4* p) {
   return v;
 }
 // Re-reads a line until both halves carry `gen` (bounded in time). false = gave up.
-__device__ __forceinline__ bool wait_line(const uint4* p, uint32_t gen, uint4& v) {
+__device__ __forceinline__ bool wait_line(const uint4* p, uint32_t gen, uint4& v,
+                                          unsigned long long budget_ns = GV_WAIT_NS) {
   if (v.y == gen && v.w == gen) return true;
   const unsigned long long t0 = global_ns();
   for (unsigned int i = 0; i < GV_SPIN_LIMIT; ++i) {
     v = ld_line(p);
     if (v.y == gen && v.w == gen) return true;
-    if ((i & 63u) == 63u && global_ns() - t0 > GV_WAIT_NS) return false;
+    if ((i & 63u) == 63u && global_ns() - t0 > budget_ns) return false;
   }
   return false;
 }
@@ -140,7 +141,8 @@ __device__ __forceinline__ bool reduce_lines(const uint4* __restrict__ base, con
 #pragma unroll
           for (int jj = 1; jj < NSRC; ++jj)
             if (jj == j) w = v[rr][jj];
-          if (!wait_line(base + ((long long)src * m_cap + c) * lines_per_row + (feat >> 2), gen, w))
+          if (!wait_line(base + ((long long)src * m_cap + c) * lines_per_row + (feat >> 2), gen, w,
+                         ok ? GV_WAIT_NS : 0ull))
             ok = false;
           add_bf2(acc, w.x);
           add_bf2(acc + 2, w.z);
@@ -189,7 +191,7 @@ __device__ __forceinline__ bool copy_final_lines(const uint4* __restrict__ fin, 
       const int i = i0 + 4 * rr;
       if (i >= n) continue;
       const int c = cols[i];
-      if (!wait_line(fin + (long long)c * lines_per_row + (feat >> 2), gen, v[rr])) ok = false;
+      if (!wait_line(fin + (long long)c * lines_per_row + (feat >> 2), gen, v[rr], ok ? GV_WAIT_NS : 0ull)) ok = false;
       *reinterpret_cast<uint2*>(out + (long long)c * ldo + feat) = make_uint2(v[rr].x, v[rr].z);
     }
   }

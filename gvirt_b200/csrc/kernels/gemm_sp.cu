@@ -115,7 +115,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         const unsigned int* f = reinterpret_cast<const unsigned int*>(static_cast<char*>(a.peers[a.rank]) +
                                                                       a.flags_off) +
                                 (size_t)tile_id * SP_MAX_RANKS + s;
-        if (!wait_ge_sys(f, gen)) atomicOr(status, GV_ST_TIMEOUT_PEER);
+        if (!wait_ge_sys(f, gen, peer_budget(status))) atomicOr(status, GV_ST_TIMEOUT_PEER);
       }
       sp_epi_bar();
       const bf16* base = reinterpret_cast<const bf16*>(static_cast<char*>(a.peers[a.rank]) + a.data_off) +
@@ -220,7 +220,7 @@ ag_gemm_kernel(const CUtensorMap* __restrict__ maps, const __grid_constant__ CUt
     if (lane == 0) {
       const unsigned int* f =
           reinterpret_cast<const unsigned int*>(static_cast<char*>(a.peers[a.rank]) + a.flags_off) + owner;
-      if (!wait_ge_sys(f, gen)) atomicOr(status, GV_ST_TIMEOUT_PEER);
+      if (!wait_ge_sys(f, gen, peer_budget(status))) atomicOr(status, GV_ST_TIMEOUT_PEER);
     }
     __syncwarp();
     // the flag was observed through the generic proxy; the tile loads go through the async proxy

@@ -24,7 +24,12 @@
 //     kernel fully overwrites every partial slot it later reads, so nothing has to be cleared
 //     between calls — but two calls whose kernels overlap on the GPU (different streams without
 //     an ordering between them) race on the array. Serialise them on one stream or with events.
-//   * Arguments and results are otherwise identical to gv_paged_attention_decode.
+//   * Arguments and results are otherwise identical to gv_paged_attention_decode. The raw
+//     metadata is not validated on the host: a sequence length beyond max_blocks * block_size or
+//     a block id outside [0, num_blocks) raises GV_ST_BAD_INDEX (32) in the status word below
+//     and the affected keys are skipped; nothing is read out of range.
+//   * The entry points may be called from several host threads; the per-device set-up is
+//     serialised internally.
 #pragma once
 #ifdef __cplusplus
 extern "C" {
@@ -42,6 +47,9 @@ int gv_paged_attention_decode_noalloc(const void* q, const void* k_cache, const 
 // Bits raised by kernels launched through the entry point above on the current device
 // (same meaning as the library-wide status word); synchronises `stream`.
 int gv_noalloc_status_read(unsigned int* host_out, void* stream);
+// Clears those bits (an asynchronous memset on `stream`): the word is sticky, so a caller that has
+// handled an error clears it before the next call it wants to check.
+int gv_noalloc_status_reset(void* stream);
 
 #ifdef __cplusplus
 }

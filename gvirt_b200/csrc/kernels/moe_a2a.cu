@@ -135,7 +135,7 @@ __global__ void a2a_recv_prepare_kernel(int* __restrict__ seg_start, int* __rest
   const int s = threadIdx.x;
   if (s < a.R) {
     const unsigned int* f = reinterpret_cast<const unsigned int*>(slab(a, a.rank) + a.flag_off) + s;
-    if (!wait_ge_sys(f, gen)) atomicOr(a.status, GV_ST_TIMEOUT_PEER);
+    if (!wait_ge_sys(f, gen, peer_budget(a.status))) atomicOr(a.status, GV_ST_TIMEOUT_PEER);
   }
   __syncthreads();
   int* cnt = reinterpret_cast<int*>(slab(a, a.rank) + a.cnt_off);
@@ -193,7 +193,7 @@ __global__ void a2a_combine_wait_kernel(A2AArgs a) {
   if (s < a.R) {
     const unsigned int* f =
         reinterpret_cast<const unsigned int*>(slab(a, a.rank) + a.flag_off) + A2A_MAX_RANKS + s;
-    if (!wait_ge_sys(f, gen)) atomicOr(a.status, GV_ST_TIMEOUT_PEER);
+    if (!wait_ge_sys(f, gen, peer_budget(a.status))) atomicOr(a.status, GV_ST_TIMEOUT_PEER);
   }
 }
 

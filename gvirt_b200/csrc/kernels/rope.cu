@@ -265,7 +265,8 @@ __global__ void rope_kvwrite_hd128_kernel(RopeArgs a, unsigned int* status) {
 // Row-tiled variant of the 128-wide kernel for long chunks: one warp per token walks all of the
 // token's heads, so the token's position, its cos / sin values (1 KB, four times the bytes of a
 // head) and its cache slot are fetched once per token instead of once per head. Lane layout,
-// rounding and rotation are those of `rope_kvwrite_hd128_kernel`. Opt-in (GVIRT_ROPE_ROWS=1).
+// rounding and rotation are those of `rope_kvwrite_hd128_kernel`. Used for chunks of 256 tokens or
+// more (80 us against 97 us on 8192 tokens x 48 heads); GVIRT_ROPE_ROWS=0 turns it off.
 __global__ void rope_kvwrite_hd128_rows_kernel(RopeArgs a, unsigned int* status) {
   pdl_wait();
   pdl_trigger();
@@ -406,7 +407,7 @@ extern "C" int gv_rope_kvwrite(void* qkv, const void* bias, const void* q_norm_w
       al(k_cache, 8) && al(v_cache, 8) && al(bias, 8) && al(q_norm_w, 8) && al(k_norm_w, 8) && al(cos_sin, 16)) {
     static const bool rows_on = [] {
       const char* e = getenv("GVIRT_ROPE_ROWS");
-      return e && e[0] && e[0] != '0';
+      return !(e && e[0] == '0');
     }();
     if (rows_on && tokens >= 256) {
       const int wpb = 4;   // one warp per token

@@ -61,33 +61,70 @@ def export_request(llm, req_id: int, release: bool = True) -> KVPayload:
     return payload
 
 
+def _check_payload(llm, payload: KVPayload, need: int) -> None:
+    """Everything that can be wrong with a payload is found here, before a block is taken."""
+    sch, runner, cfg = llm.scheduler, llm.runner, llm.cfg
+    from .scheduler import validate_request
+    total = len(payload.prompt) + len(payload.output)
+    validate_request(list(payload.prompt), payload.params, cfg.max_seq_len, cfg.vocab_size)
+    for t in payload.output:
+        if not isinstance(t, int) or not 0 <= t < cfg.vocab_size:
+            raise ValueError(f"output token id {t!r} is outside [0, {cfg.vocab_size})")
+    if total > cfg.max_seq_len:
+        raise ValueError(f"request of {total} tokens exceeds max_seq_len {cfg.max_seq_len}")
+    if payload.num_computed != total - 1 and payload.num_computed != len(payload.prompt):
+        raise ValueError(f"num_computed {payload.num_computed} does not match a request of {total} tokens")
+    if len(payload.layers) != len(runner.kv_caches):
+        raise ValueError(f"payload has {len(payload.layers)} layers, the engine {len(runner.kv_caches)}")
+    for li, (caches, src) in enumerate(zip(runner.kv_caches, payload.layers)):
+        if len(src) != len(caches):
+            raise ValueError(f"layer {li}: payload has {len(src)} tensors, the engine {len(caches)}")
+        linear = cfg.layer_is_linear_attn(li)
+        for c, t in zip(caches, src):
+            if not isinstance(t, torch.Tensor):
+                raise ValueError(f"layer {li}: not a tensor")
+            want = tuple(c.shape[1:]) if linear else (need,) + tuple(c.shape[1:])
+            if tuple(t.shape) != want:
+                raise ValueError(f"layer {li}: payload tensor {tuple(t.shape)}, expected {want}")
+            if t.dtype != c.dtype:
+                raise ValueError(f"layer {li}: payload dtype {t.dtype}, engine {c.dtype}")
+
+
 def import_request(llm, payload: KVPayload) -> int:
-    """Admit a request whose KV was computed elsewhere; it joins the next decode step."""
+    """Admit a request whose KV was computed elsewhere; it joins the next decode step. The payload
+    is validated against this engine (lengths, layer count, tensor shapes and dtypes) before any
+    block is allocated, and a failure after the allocation returns the blocks and the state slot."""
     sch, runner, cfg = llm.scheduler, llm.runner, llm.cfg
     if payload.block_size != cfg.block_size:
         raise ValueError(f"block size mismatch: payload {payload.block_size}, engine {cfg.block_size}")
+    need = (payload.num_computed + cfg.block_size - 1) // cfg.block_size
+    _check_payload(llm, payload, need)
     if len(sch.running) >= cfg.max_batch_size:
         raise RuntimeError("decode batch is full")
+    if sch.uses_state_slots and not sch.free_state_slots:
+        raise RuntimeError("no free recurrent-state slot for the imported request")
     rid = llm._next_id
     llm._next_id += 1
     req = Request(rid, list(payload.prompt), payload.params, output=list(payload.output))
     tokens = req.all_tokens
     if sch.bm.allocate(rid, tokens) < 0:
         raise RuntimeError("not enough free KV blocks for the imported request")
-    need = (payload.num_computed + cfg.block_size - 1) // cfg.block_size
-    blocks = list(sch.bm.block_table(rid))[:need]
-    idx = torch.tensor(blocks, dtype=torch.long, device=runner.device)
-    if sch.uses_state_slots:
-        req.state_slot = sch.free_state_slots.pop()
-    for li, (caches, src) in enumerate(zip(runner.kv_caches, payload.layers)):
-        if cfg.layer_is_linear_attn(li):
-            for c, t in zip(caches, src):
-                c[req.state_slot].copy_(t.to(c.device))
-        else:
-            for c, t in zip(caches, src):
-                if t.shape[0] != need:
-                    raise ValueError(f"layer {li}: payload has {t.shape[0]} blocks, expected {need}")
-                c.index_copy_(0, idx, t.to(c.device, c.dtype))
+    try:
+        blocks = list(sch.bm.block_table(rid))[:need]
+        idx = torch.tensor(blocks, dtype=torch.long, device=runner.device)
+        if sch.uses_state_slots:
+            req.state_slot = sch.free_state_slots.pop()
+        for li, (caches, src) in enumerate(zip(runner.kv_caches, payload.layers)):
+            if cfg.layer_is_linear_attn(li):
+                for c, t in zip(caches, src):
+                    c[req.state_slot].copy_(t.to(c.device))
+            else:
+                for c, t in zip(caches, src):
+                    c.index_copy_(0, idx, t.to(c.device, c.dtype))
+    except BaseException:
+        sch.bm.release(rid)
+        sch._free_slot(req)
+        raise
     req.num_computed = payload.num_computed
     import time
     req.arrival = time.perf_counter()

@@ -44,6 +44,41 @@ class SamplingParams:
         return self.presence_penalty != 0.0 or self.frequency_penalty != 0.0 or self.repetition_penalty != 1.0
 
 
+def validate_request(prompt, params: "SamplingParams", max_seq_len: int, vocab_size: int) -> None:
+    """Raise ``ValueError`` for a request that no engine step could run. Called on the client side
+    of the serving engine (the HTTP layer answers 400) so that a malformed request never reaches
+    the engine thread: token ids outside the vocabulary would index logits and embedding rows out
+    of range on the device, and a request longer than ``max_seq_len`` has no block-table row."""
+    import math
+    n = len(prompt)
+    if n == 0:
+        raise ValueError("empty prompt")
+    if not isinstance(params.max_tokens, int) or params.max_tokens < 1:
+        raise ValueError(f"max_tokens must be a positive integer, got {params.max_tokens!r}")
+    if n + params.max_tokens > max_seq_len:
+        raise ValueError(f"prompt of {n} tokens + max_tokens {params.max_tokens} exceeds max_seq_len {max_seq_len}")
+    for name, ids in (("prompt", prompt), ("stop_token_ids", params.stop_token_ids)):
+        for t in ids:
+            if not isinstance(t, int) or isinstance(t, bool) or not 0 <= t < vocab_size:
+                raise ValueError(f"{name}: token id {t!r} is outside [0, {vocab_size})")
+    for name in ("temperature", "top_p", "presence_penalty", "frequency_penalty", "repetition_penalty"):
+        v = getattr(params, name)
+        if not isinstance(v, (int, float)) or not math.isfinite(v):
+            raise ValueError(f"{name} must be a finite number, got {v!r}")
+    if params.temperature < 0:
+        raise ValueError(f"temperature must be >= 0, got {params.temperature}")
+    if not 0 < params.top_p <= 1:
+        raise ValueError(f"top_p must be in (0, 1], got {params.top_p}")
+    if not isinstance(params.top_k, int) or params.top_k < 0:
+        raise ValueError(f"top_k must be a non-negative integer, got {params.top_k!r}")
+    if params.repetition_penalty <= 0:
+        raise ValueError(f"repetition_penalty must be > 0, got {params.repetition_penalty}")
+    if not -2.0 <= params.presence_penalty <= 2.0 or not -2.0 <= params.frequency_penalty <= 2.0:
+        raise ValueError("presence_penalty and frequency_penalty must be in [-2, 2]")
+    if not isinstance(params.logprobs, int) or not 0 <= params.logprobs <= 20:
+        raise ValueError(f"logprobs must be in [0, 20], got {params.logprobs!r}")
+
+
 @dataclass
 class MultiModalInputs:
     """Pre-computed embeddings for some prompt positions (image / video patches from a vision

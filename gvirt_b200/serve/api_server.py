@@ -75,6 +75,12 @@ def build_app(engine: AsyncEngine, model_name: str = "gvirt"):
                 "top_logprobs": [{name(t): v for t, v in top} for _, top in r.logprobs]}
 
     def _params(body: dict) -> SamplingParams:
+        try:
+            return _params_unchecked(body)
+        except (TypeError, ValueError) as e:        # "max_tokens": "many", "stop_token_ids": 5, ...
+            raise HTTPException(400, f"bad sampling parameter: {e}")
+
+    def _params_unchecked(body: dict) -> SamplingParams:
         return SamplingParams(max_tokens=int(body.get("max_tokens", 16)),
                               temperature=float(body.get("temperature", 0.0)),
                               top_k=int(body.get("top_k", 0)), top_p=float(body.get("top_p", 1.0)),
@@ -188,8 +194,13 @@ def build_app(engine: AsyncEngine, model_name: str = "gvirt"):
                 raise HTTPException(400, "streaming takes a single prompt")
             loop = asyncio.get_running_loop()
             q: asyncio.Queue = asyncio.Queue()
-            fut = engine.submit(prompts[0], sp, stop=stop,
-                                on_token=lambda _r, tok: loop.call_soon_threadsafe(q.put_nowait, tok))
+            try:
+                fut = engine.submit(prompts[0], sp, stop=stop,
+                                    on_token=lambda _r, tok: loop.call_soon_threadsafe(q.put_nowait, tok))
+            except ValueError as e:
+                raise HTTPException(400, str(e))
+            except QueueFull as e:
+                raise HTTPException(429, str(e))
             fut.add_done_callback(lambda f: loop.call_soon_threadsafe(q.put_nowait, None))
 
             async def gen():
@@ -267,8 +278,13 @@ def build_app(engine: AsyncEngine, model_name: str = "gvirt"):
         if body.get("stream"):
             loop = asyncio.get_running_loop()
             q: asyncio.Queue = asyncio.Queue()
-            fut = engine.submit(ids, sp, stop=stop,
-                                on_token=lambda _r, t: loop.call_soon_threadsafe(q.put_nowait, t))
+            try:
+                fut = engine.submit(ids, sp, stop=stop,
+                                    on_token=lambda _r, t: loop.call_soon_threadsafe(q.put_nowait, t))
+            except ValueError as e:
+                raise HTTPException(400, str(e))
+            except QueueFull as e:
+                raise HTTPException(429, str(e))
             fut.add_done_callback(lambda f: loop.call_soon_threadsafe(q.put_nowait, None))
 
             async def gen():

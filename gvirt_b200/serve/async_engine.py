@@ -30,7 +30,7 @@ from dataclasses import dataclass, field
 from typing import Callable, Dict, List, Optional, Sequence
 
 from ..engine.llm import LLM
-from ..engine.scheduler import Request, SamplingParams
+from ..engine.scheduler import Request, SamplingParams, validate_request
 
 
 @dataclass
@@ -196,7 +196,10 @@ def follower_loop(llm: LLM, control_group=None) -> int:
             return steps
         for gid, dp_rank, prompt, params in ev["new"]:
             if dp_rank == ctx.dp_rank:
-                owned.add(gid, prompt, SamplingParams(**params))
+                try:
+                    owned.add(gid, prompt, SamplingParams(**params))
+                except (ValueError, RuntimeError):
+                    pass        # rank 0 validated the same request with the same limits and dropped it
         for gid in ev["abort"]:
             owned.abort(gid)
         if ev["step"]:
@@ -258,16 +261,15 @@ class AsyncEngine:
             raise NotImplementedError("KV export over HTTP is for single-process replicas")
         if self.error is not None:
             raise RuntimeError("engine loop has stopped") from self.error
-        if len(prompt) == 0:
-            raise ValueError("empty prompt")
-        if len(prompt) + 1 > self.llm.cfg.max_seq_len:
-            raise ValueError(f"prompt of {len(prompt)} tokens exceeds max_seq_len {self.llm.cfg.max_seq_len}")
+        params = params or SamplingParams()
+        prompt = list(prompt)
+        validate_request(prompt, params, self.llm.cfg.max_seq_len, self.llm.cfg.vocab_size)
         fut: Future = Future()
         with self._lock:
             if self.max_pending and self._pending >= self.max_pending:
                 raise QueueFull(f"{self._pending} requests pending (limit {self.max_pending})")
             self._pending += 1
-            p = _Pending(list(prompt), params or SamplingParams(), fut, on_token,
+            p = _Pending(prompt, params, fut, on_token,
                          stop=tuple(x for x in stop if x), export=export_after_prefill)
             if timeout_s is not None:
                 p.deadline = p.submitted + float(timeout_s)
@@ -344,7 +346,12 @@ class AsyncEngine:
                 self._owned.reqs[gid] = [req, 0]
                 p.payload = None
             elif dp_rank == my_dp:
-                req = self._owned.add(gid, p.prompt, p.params)
+                try:
+                    req = self._owned.add(gid, p.prompt, p.params)
+                except (ValueError, RuntimeError) as e:     # a bad request fails alone, the engine goes on
+                    self._load[dp_rank] -= 1
+                    p.future.set_exception(e)
+                    continue
             else:
                 req = _Remote(gid, p.prompt, p.params)
             p.future.request_id = gid

@@ -40,6 +40,7 @@ class TorchLlama:
             self.layers.append(dict(
                 n1=torch.ones(H, dtype=dt, device=dev), n2=torch.ones(H, dtype=dt, device=dev),
                 qkv=w((self.nq + 2 * self.nkv) * hd, H), o=w(H, self.nq * hd),
+                b_qkv=w((self.nq + 2 * self.nkv) * hd) if getattr(cfg, "qkv_bias", False) else None,
                 gu=w(2 * cfg.intermediate_size // tp, H), down=w(H, cfg.intermediate_size // tp)))
         self.norm = torch.ones(H, dtype=dt, device=dev)
         self.k = [torch.zeros(batch, self.nkv, max_len, hd, dtype=dt, device=dev) for _ in range(cfg.num_layers)]
@@ -63,6 +64,8 @@ class TorchLlama:
         for i, L in enumerate(self.layers):
             h = self._rms(x, L["n1"])
             qkv = h @ L["qkv"].t()
+            if L["b_qkv"] is not None:
+                qkv = qkv + L["b_qkv"]
             q, k, v = qkv.split([self.nq * hd, self.nkv * hd, self.nkv * hd], -1)
             q = _rope(q.view(B, S, self.nq, hd), cos, sin).transpose(1, 2)
             k = _rope(k.view(B, S, self.nkv, hd), cos, sin).transpose(1, 2)
@@ -70,8 +73,17 @@ class TorchLlama:
             self.k[i][:, :, start:start + S] = k
             self.v[i][:, :, start:start + S] = v
             kk, vv = self.k[i][:, :, :start + S], self.v[i][:, :, :start + S]
-            o = TF.scaled_dot_product_attention(q, kk, vv, is_causal=(S > 1), enable_gqa=True)
-            o = o.transpose(1, 2).reshape(B, S, self.nq * hd) @ L["o"].t()
+            if S == 1:
+                # decode: the query heads that share a kv head become the rows of one attention
+                # problem per kv head ([B, nkv, G, hd] against [B, nkv, L, hd]); this shape takes a
+                # fused SDPA kernel, whereas enable_gqa on a one-token query falls back to the
+                # unfused math path
+                G = self.nq // self.nkv
+                o = TF.scaled_dot_product_attention(q.reshape(B, self.nkv, G, hd), kk, vv, is_causal=False)
+                o = o.reshape(B, 1, self.nq * hd) @ L["o"].t()
+            else:
+                o = TF.scaled_dot_product_attention(q, kk, vv, is_causal=True, enable_gqa=True)
+                o = o.transpose(1, 2).reshape(B, S, self.nq * hd) @ L["o"].t()
             if ctx.tp > 1:
                 dist.all_reduce(o, group=ctx.tp_group)
             x = x + o
@@ -91,9 +103,13 @@ class TorchLlama:
         return logits.argmax(-1)
 
 
-def run_floor(cfg, ctx, B, P, K, W):
+def run_floor(cfg, ctx, B, P, K, W, advance=0):
+    """`advance`: decode positions skipped after the warm-up so that the timed steps sit at the
+    same context as the main arm's (the skipped cache rows stay zero: same bytes, same work)."""
+    if cfg.is_moe or cfg.attn_type.name != "MHA":
+        raise SystemExit("--impl torch covers the dense MHA decoders (Llama, Qwen2, Qwen2.5)")
     dev = ctx.device
-    max_len = P + 2 * (K + W) + 16
+    max_len = P + 2 * (K + W) + advance + 16
     model = TorchLlama(cfg, ctx, B, max_len)
     g = torch.Generator().manual_seed(1234)
     prompts = torch.randint(0, cfg.vocab_size, (B, P), generator=g)
@@ -120,6 +136,7 @@ def run_floor(cfg, ctx, B, P, K, W):
     for _ in range(W):
         nxt = model.forward(nxt[:, None], pos)
         pos += 1
+    pos += advance
     barrier()
     # end to end: token ids come from pinned host memory each step, result is read back
     host_tok.copy_(nxt)
@@ -151,7 +168,8 @@ def run_floor(cfg, ctx, B, P, K, W):
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic", "impl": "torch",
             "config": {"model": cfg.name, "global_batch": B, "seq_len": P, "parallelism": f"tp{ctx.world}",
-                       "layers": cfg.num_layers, "note": "PyTorch eager: cuBLAS + SDPA + NCCL, dense KV cache"},
+                       "layers": cfg.num_layers, "decode_context": pos,
+                       "note": "PyTorch eager: cuBLAS + SDPA + NCCL, dense KV cache"},
             "e2e": {"value": round(B * K / (e2e_ms / 1e3), 1), "unit": "tok/s", "ms_per_step": round(e2e_ms / K, 4),
                     "h2d_bytes_per_step": B * 8, "d2h_bytes_per_step": B * 8},
             "gpu_launches": 0, "prefill_tok_s": round(B * P / prefill_s, 1)}

@@ -91,8 +91,6 @@ def test_linear_swiglu_epilogue(M, I, K):
     status_ok()
 
 
-@pytest.mark.skipif(__import__("os").environ.get("GVIRT_TEST_PERSISTENT_GEMM", "") != "1",
-                    reason="opt in with GVIRT_TEST_PERSISTENT_GEMM=1: gemm_persist.cu has not been run on a GPU yet")
 @pytest.mark.parametrize("M,N,K,bias", [(1024, 512, 256, False), (1024, 256, 64, True), (1100, 384, 512, True),
                                         (2048, 6144, 4096, False), (8192, 4096, 4096, False), (4096, 1000, 1032, True)])
 def test_gemm_persistent_token_major(M, N, K, bias):

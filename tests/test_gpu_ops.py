@@ -166,8 +166,6 @@ def test_sampling():
     assert torch.equal(lf.gather(1, s.long()[:, None])[:, 0][::2], mx[::2])
 
 
-@pytest.mark.skipif(__import__("os").environ.get("GVIRT_ROPE_ROWS", "") != "1",
-                    reason="opt in with GVIRT_ROPE_ROWS=1: the row-tiled RoPE kernel has not been run on a GPU yet")
 @pytest.mark.parametrize("bias,qkn,mode", [(False, False, 0), (True, True, 0), (False, False, 1), (False, True, 2)])
 def test_rope_kvwrite_row_tiled(bias, qkn, mode):
     """One warp per token (chunks of 256 tokens or more): same results as the per-head kernels,

@@ -151,22 +151,24 @@ def test_multi_gpu(mode):
     _run(mode, min(world, n))
 
 
-def test_peer_that_never_arrives_times_out_and_context_survives():
+@pytest.mark.parametrize("rows", [8, 512])
+def test_peer_that_never_arrives_times_out_and_context_survives(rows):
     """Failure detection on the device: a push all-reduce is told it has a peer, but nothing ever
     writes that peer's lines. The bounded poll gives up (about two seconds), the kernel returns,
-    the status word carries the PEER bit, and the same context runs the next kernel normally."""
+    the status word carries the PEER bit, and the same context runs the next kernel normally.
+    The budget is per launch: with 512 rows on one CTA every thread owns many lines, and the
+    launch must still end after one wait, not one wait per line."""
     import time
     from gvirt_b200 import _native
     heap = _heap()
     status_ok()
-    x = torch.randn(8, 128, device=DEV).bfloat16()
+    x = torch.randn(rows, 128, device=DEV).bfloat16()
     out = torch.empty_like(x)
     n = x.numel()
     lines = n * 2 // 8
-    ch = heap.channel("timeout_probe", 16 * 2 * 1024, 1)
+    ch = heap.channel(f"timeout_probe_{rows}", 16 * 3 * max(lines, 1024), 1)
     fake_peers = torch.tensor([heap.slab.data_ptr(), heap.slab.data_ptr() + (128 << 20)], dtype=torch.int64,
                               device=DEV)                 # "rank 1" = an unused half of the same slab
-    assert lines <= 1024
     t0 = time.time()
     _native.call("collective", 4, 0, x, out, n, fake_peers, ch.flags_off, ch.data_off, ch.data_stride,
                  ch.state, 0, 2, 1)
@@ -174,7 +176,7 @@ def test_peer_that_never_arrives_times_out_and_context_survives():
     dt = time.time() - t0
     st = _native.read_status()
     assert st & 8, _native.describe_status(st)            # GV_ST_TIMEOUT_PEER
-    assert 1.0 < dt < 30.0, dt
+    assert 1.0 < dt < 6.0, dt
     _native.reset_status()
     y = heap.all_reduce(x.clone())
     assert torch.equal(y, x)

@@ -239,7 +239,7 @@ def test_queue_limit_and_request_timeout():
     from gvirt_b200.serve.async_engine import QueueFull
     eng = AsyncEngine(_llm(), max_pending=2)
     try:
-        long = SamplingParams(max_tokens=100, ignore_eos=True)
+        long = SamplingParams(max_tokens=80, ignore_eos=True)
         a = eng.submit(PROMPTS[0], long, timeout_s=0.15)
         b = eng.submit(PROMPTS[1], long)
         with pytest.raises(QueueFull):
@@ -275,5 +275,79 @@ def test_bad_kv_payload_fails_its_request_not_the_engine():
         ok = eng.submit(PROMPTS[1], sp).result(timeout=60)
         assert len(ok.output_ids) == 6 and eng.error is None
         assert eng.llm.scheduler.bm.num_free_blocks == eng.llm.num_blocks
+    finally:
+        eng.shutdown()
+
+
+def test_truncated_kv_payload_leaks_nothing():
+    """Payloads with missing layers, a wrong tensor shape, a wrong dtype or an inconsistent token
+    count are refused before any block is taken: free blocks and sequence count stay as they were."""
+    import copy
+    from gvirt_b200.engine.kv_transfer import export_request
+    src = _llm()
+    sp = SamplingParams(max_tokens=6, ignore_eos=True)
+    rid = src.add_request(PROMPTS[2], sp)
+    src.step()
+    good = export_request(src, rid)
+    eng = AsyncEngine(_llm())
+    try:
+        bm = eng.llm.scheduler.bm
+        free0 = bm.num_free_blocks
+        bad = []
+        p = copy.copy(good); p.layers = good.layers[:1]; bad.append(p)
+        p = copy.copy(good); p.layers = [tuple(t[:, :1] for t in ts) for ts in good.layers]; bad.append(p)
+        p = copy.copy(good); p.layers = [tuple(t.double() for t in ts) for ts in good.layers]; bad.append(p)
+        p = copy.copy(good); p.num_computed = good.num_computed + 5; bad.append(p)
+        p = copy.copy(good); p.output = [10 ** 9]; bad.append(p)
+        for _ in range(3):
+            for p in bad:
+                with pytest.raises(ValueError):
+                    eng.submit_payload(p).result(timeout=30)
+        assert bm.num_free_blocks == free0 and not eng.llm.scheduler.running
+        done = eng.submit_payload(good).result(timeout=60)          # the intact payload still decodes
+        assert len(done.output_ids) == 6 and eng.error is None
+        assert bm.num_free_blocks == eng.llm.num_blocks
+    finally:
+        eng.shutdown()
+
+
+def test_malformed_requests_are_refused_and_the_engine_keeps_serving(golden):
+    """max_tokens beyond the context window, token ids outside the vocabulary and out-of-range
+    sampling parameters raise on the client side (HTTP 400); the next request is served."""
+    eng = AsyncEngine(_llm())
+    try:
+        vocab = eng.llm.cfg.vocab_size
+        ok = SamplingParams(max_tokens=12, ignore_eos=True)
+        cases = [([1, 2, 3, 4, 5], SamplingParams(max_tokens=1000)),
+                 ([1, vocab], ok), ([-1], ok), ([1, 2], SamplingParams(max_tokens=0)),
+                 ([1, 2], SamplingParams(max_tokens=4, stop_token_ids=(vocab + 7,))),
+                 ([1, 2], SamplingParams(max_tokens=4, top_p=0.0)), ([1, 2], SamplingParams(max_tokens=4, top_k=-3)),
+                 ([1, 2], SamplingParams(max_tokens=4, temperature=float("nan"))),
+                 ([1, 2], SamplingParams(max_tokens=4, repetition_penalty=0.0)),
+                 ([1, 2], SamplingParams(max_tokens=4, presence_penalty=50.0))]
+        for prompt, sp in cases:
+            with pytest.raises(ValueError):
+                eng.submit(prompt, sp)
+        assert eng.error is None
+        assert eng.submit(PROMPTS[0], ok).result(timeout=60).output_ids == golden[0]
+        # a request that passes the client-side check but is refused at admission fails alone
+        real_add = eng._owned.add
+        def boom(gid, prompt, params):
+            eng._owned.add = real_add
+            raise ValueError("refused at admission")
+        eng._owned.add = boom
+        with pytest.raises(ValueError):
+            eng.submit(PROMPTS[1], ok).result(timeout=30)
+        assert eng.error is None and sum(eng._load) == 0
+        assert eng.submit(PROMPTS[1], ok).result(timeout=60).output_ids == golden[1]
+        from starlette.testclient import TestClient
+        client = TestClient(build_app(eng, "tiny"))
+        for body in ({"prompt": [1, 2, 3], "max_tokens": 1000}, {"prompt": [1, vocab + 1], "max_tokens": 4},
+                     {"prompt": [1, 2], "max_tokens": "many"}, {"prompt": [1, 2], "max_tokens": 4, "top_p": 7},
+                     {"prompt": [1, 2], "max_tokens": 1000, "stream": True}):
+            assert client.post("/v1/completions", json=body).status_code == 400, body
+        assert client.get("/health").status_code == 200
+        r = client.post("/v1/completions", json={"prompt": PROMPTS[0], "max_tokens": 12, "ignore_eos": True})
+        assert r.status_code == 200 and r.json()["choices"][0]["token_ids"] == golden[0]
     finally:
         eng.shutdown()

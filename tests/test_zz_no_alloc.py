@@ -99,3 +99,30 @@ def test_noalloc_rejects_oversized_request():
     rc, _ = _noalloc(lib, q, kc, vc, bt, sl, nq, nkv, hd, bs, 16, nb)  # 64*32*16*129*4 B > 8 MiB
     assert rc == -4
     assert b"exceeds" in lib.gv_last_error()
+
+
+def test_noalloc_flags_a_length_beyond_the_block_table_and_the_flag_can_be_cleared():
+    """Raw callers bypass the host-side metadata checks, so the kernel itself must refuse a
+    sequence length that runs past the block-table row: the keys beyond the row are skipped (no
+    read outside the table), GV_ST_BAD_INDEX (32) is raised, and `gv_noalloc_status_reset` clears
+    the sticky word so that the next, valid call reads 0 again."""
+    lib = _lib()
+    nq, nkv, hd, bs = 8, 2, 128, 128
+    lens = [200, 260]
+    q, kc, vc, bt, sl, nb = _case(14, len(lens), nq, nkv, hd, bs, lens)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    st = ctypes.c_uint(0)
+    bad = sl.clone()
+    bad[1] = bt.shape[1] * bs + 40          # 40 keys past the end of the row
+    rc, got = _noalloc(lib, q, kc, vc, bt, bad, nq, nkv, hd, bs, 2, nb)
+    assert rc == 0, lib.gv_last_error()
+    assert lib.gv_noalloc_status_read(ctypes.byref(st), stream) == 0
+    assert st.value & 32
+    assert torch.isfinite(got.float()).all()
+    assert lib.gv_noalloc_status_reset(stream) == 0
+    want = _regular(lib, q, kc, vc, bt, sl, nq, nkv, hd, bs, 2, nb)
+    rc, got = _noalloc(lib, q, kc, vc, bt, sl, nq, nkv, hd, bs, 2, nb)
+    assert rc == 0, lib.gv_last_error()
+    assert lib.gv_noalloc_status_read(ctypes.byref(st), stream) == 0
+    assert st.value == 0
+    assert (got.float() - want.float()).abs().max().item() <= 1e-2
