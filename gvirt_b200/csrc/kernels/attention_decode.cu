@@ -34,7 +34,7 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc,
                     const int* __restrict__ seq_lens, bf16* __restrict__ out,
                     float* __restrict__ part_o, float* __restrict__ part_lse, int nq, int nkv,
                     int block_size, int max_blocks, int nsplit, float scale_log2,
-                    long long num_blocks, unsigned int* status) {
+                    long long num_blocks, unsigned int* status, int* counters) {
   constexpr int ROW_BYTES = HD * 2;
   constexpr int CH = ROW_BYTES / 16;            // 16-byte chunks per row
   constexpr int TILE_BYTES = DEC_TOK * ROW_BYTES;
@@ -242,6 +242,40 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc,
       if (d == 0) part_lse[head * nsplit + split] = L > 0.f ? M + log2f(L) : -INFINITY;
     }
   }
+  if (nsplit == 1 || counters == nullptr) return;
+  // ---- in-kernel merge: the CTA that publishes the last split of this (request, kv head) merges
+  // all of them, so no second launch is needed. A ticket counter per (request, kv head) counts the
+  // finished splits; it returns to zero for the next launch. Nobody waits on anybody.
+  __shared__ int s_last;
+  __syncthreads();                   // every thread's partials are written ...
+  if (threadIdx.x == 0) {
+    __threadfence();                 // ... and (fences are cumulative) visible device-wide ...
+    int* cnt = counters + (long long)b * nkv + kvh;
+    const int old = atomicAdd(cnt, 1);      // ... before this CTA's ticket is
+    s_last = old == nsplit - 1;
+    if (s_last) {
+      *cnt = 0;
+      __threadfence();
+    }
+  }
+  __syncthreads();
+  if (!s_last) return;
+  for (int idx = threadIdx.x; idx < G * HD; idx += blockDim.x) {
+    const int row = idx / HD, d = idx % HD;
+    const long long head = (long long)b * nq + (long long)kvh * G + row;
+    const float* lse = part_lse + head * nsplit;
+    float M = -INFINITY;
+    for (int sp = 0; sp < nsplit; ++sp) M = fmaxf(M, __ldcg(lse + sp));
+    float W = 0.f, acc = 0.f;
+    for (int sp = 0; sp < nsplit; ++sp) {
+      const float l = __ldcg(lse + sp);
+      if (l == -INFINITY) continue;
+      const float w = exp2f(l - M);
+      W += w;
+      acc += w * __ldcg(part_o + (head * nsplit + sp) * HD + d);
+    }
+    out[head * HD + d] = f2bf(W > 0.f ? acc / W : 0.f);
+  }
 }
 
 template <int HD>
@@ -271,7 +305,7 @@ template <int HD, int TOK = DEC_TOK, int STAGES = DEC_STAGES>
 static int launch_decode(const void* q, const void* kc, const void* vc, const void* bt,
                          const void* lens, void* out, void* part_o, void* part_lse, int batch,
                          int nq, int nkv, int block_size, int max_blocks, int nsplit, float scale,
-                         long long num_blocks, cudaStream_t st) {
+                         long long num_blocks, cudaStream_t st, int* counters = nullptr) {
   constexpr int SMEM = DEC_WARPS * STAGES * 2 * TOK * HD * 2;
   static_assert(STAGES * 2 * TOK * HD * 2 >= (16 * HD + 32) * 4, "merge area must fit");
   auto kern = paged_decode_kernel<HD, TOK, STAGES>;
@@ -288,10 +322,10 @@ static int launch_decode(const void* q, const void* kc, const void* vc, const vo
   launch_pdl(kern, grid, dim3(DEC_WARPS * 32), SMEM, st, (const bf16*)q, (const bf16*)kc,
              (const bf16*)vc, (const int*)bt, (const int*)lens, (bf16*)out, (float*)part_o,
              (float*)part_lse, nq, nkv, block_size, max_blocks, nsplit,
-             scale * 1.4426950408889634f, num_blocks, status_word());
+             scale * 1.4426950408889634f, num_blocks, status_word(), counters);
   int rc = check_launch("paged_decode");
   if (rc != GV_OK) return rc;
-  if (nsplit > 1) {
+  if (nsplit > 1 && counters == nullptr) {
     launch_pdl(decode_merge_kernel<HD>, dim3((unsigned)(batch * nq)), dim3(HD < 128 ? HD : 128), 0,
                st, (const float*)part_o, (const float*)part_lse, (bf16*)out, nsplit);
     rc = check_launch("decode_merge");
@@ -310,13 +344,13 @@ template <int HD>
 static int dispatch_variant(long long variant, const void* q, const void* kc, const void* vc,
                             const void* bt, const void* lens, void* out, void* po, void* pl, int batch,
                             int nq, int nkv, int bs, int mb, int ns, float scale, long long nb,
-                            cudaStream_t st) {
+                            cudaStream_t st, int* cnt = nullptr) {
   switch (variant) {
-    case 1: return launch_decode<HD, 16, 2>(q, kc, vc, bt, lens, out, po, pl, batch, nq, nkv, bs, mb, ns, scale, nb, st);
-    case 2: return launch_decode<HD, 16, 3>(q, kc, vc, bt, lens, out, po, pl, batch, nq, nkv, bs, mb, ns, scale, nb, st);
-    case 3: return launch_decode<HD, 16, 4>(q, kc, vc, bt, lens, out, po, pl, batch, nq, nkv, bs, mb, ns, scale, nb, st);
-    case 4: return launch_decode<HD, 32, 3>(q, kc, vc, bt, lens, out, po, pl, batch, nq, nkv, bs, mb, ns, scale, nb, st);
-    default: return launch_decode<HD, 32, 2>(q, kc, vc, bt, lens, out, po, pl, batch, nq, nkv, bs, mb, ns, scale, nb, st);
+    case 1: return launch_decode<HD, 16, 2>(q, kc, vc, bt, lens, out, po, pl, batch, nq, nkv, bs, mb, ns, scale, nb, st, cnt);
+    case 2: return launch_decode<HD, 16, 3>(q, kc, vc, bt, lens, out, po, pl, batch, nq, nkv, bs, mb, ns, scale, nb, st, cnt);
+    case 3: return launch_decode<HD, 16, 4>(q, kc, vc, bt, lens, out, po, pl, batch, nq, nkv, bs, mb, ns, scale, nb, st, cnt);
+    case 4: return launch_decode<HD, 32, 3>(q, kc, vc, bt, lens, out, po, pl, batch, nq, nkv, bs, mb, ns, scale, nb, st, cnt);
+    default: return launch_decode<HD, 32, 2>(q, kc, vc, bt, lens, out, po, pl, batch, nq, nkv, bs, mb, ns, scale, nb, st, cnt);
   }
 }
 
@@ -324,13 +358,11 @@ static long long g_decode_variant = 2;  // (16 tokens, 3 stages): two CTAs per S
 
 extern "C" void gv_set_decode_variant(long long v) { g_decode_variant = v; }
 
-extern "C" int gv_paged_attention_decode(const void* q, const void* k_cache, const void* v_cache,
-                                         const void* block_tables, const void* seq_lens, void* out,
-                                         void* part_o, void* part_lse, long long batch,
-                                         long long nq, long long nkv, long long head_dim,
-                                         long long block_size, long long max_blocks,
-                                         long long nsplit, float scale, long long num_blocks,
-                                         void* stream) {
+static int decode_any(const void* q, const void* k_cache, const void* v_cache,
+                      const void* block_tables, const void* seq_lens, void* out, void* part_o,
+                      void* part_lse, void* counters, long long batch, long long nq, long long nkv,
+                      long long head_dim, long long block_size, long long max_blocks,
+                      long long nsplit, float scale, long long num_blocks, void* stream) {
   if (!q || !k_cache || !v_cache || !block_tables || !seq_lens || !out) return GV_EINVAL;
   if (batch == 0) return GV_OK;
   if (nkv <= 0 || nq % nkv != 0 || nq / nkv > 16 || nsplit < 1) return GV_EINVAL;
@@ -342,14 +374,41 @@ extern "C" int gv_paged_attention_decode(const void* q, const void* k_cache, con
     case 64:
       return dispatch_variant<64>(g_decode_variant, q, k_cache, v_cache, block_tables, seq_lens, out,
                                   part_o, part_lse, (int)batch, (int)nq, (int)nkv, (int)block_size,
-                                  (int)max_blocks, (int)nsplit, scale, num_blocks, st);
+                                  (int)max_blocks, (int)nsplit, scale, num_blocks, st, (int*)counters);
     case 128:
       return dispatch_variant<128>(g_decode_variant, q, k_cache, v_cache, block_tables, seq_lens, out,
                                    part_o, part_lse, (int)batch, (int)nq, (int)nkv, (int)block_size,
-                                   (int)max_blocks, (int)nsplit, scale, num_blocks, st);
+                                   (int)max_blocks, (int)nsplit, scale, num_blocks, st, (int*)counters);
     default:
       return GV_EUNSUPPORTED;
   }
+}
+
+extern "C" int gv_paged_attention_decode(const void* q, const void* k_cache, const void* v_cache,
+                                         const void* block_tables, const void* seq_lens, void* out,
+                                         void* part_o, void* part_lse, long long batch,
+                                         long long nq, long long nkv, long long head_dim,
+                                         long long block_size, long long max_blocks,
+                                         long long nsplit, float scale, long long num_blocks,
+                                         void* stream) {
+  return decode_any(q, k_cache, v_cache, block_tables, seq_lens, out, part_o, part_lse, nullptr, batch,
+                    nq, nkv, head_dim, block_size, max_blocks, nsplit, scale, num_blocks, stream);
+}
+
+// Same, with the split merge done inside the kernel by whichever CTA finishes a (request, kv head)
+// last: one launch instead of two. `counters`: batch * nkv int32, zero before the first call; the
+// kernel leaves them zero again, so one array serves every call that is ordered on its stream.
+extern "C" int gv_paged_attention_decode_merged(const void* q, const void* k_cache,
+                                                const void* v_cache, const void* block_tables,
+                                                const void* seq_lens, void* out, void* part_o,
+                                                void* part_lse, void* counters, long long batch,
+                                                long long nq, long long nkv, long long head_dim,
+                                                long long block_size, long long max_blocks,
+                                                long long nsplit, float scale,
+                                                long long num_blocks, void* stream) {
+  if (nsplit > 1 && !counters) return GV_EINVAL;
+  return decode_any(q, k_cache, v_cache, block_tables, seq_lens, out, part_o, part_lse, counters, batch,
+                    nq, nkv, head_dim, block_size, max_blocks, nsplit, scale, num_blocks, stream);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -430,7 +489,8 @@ static int launch_decode_noalloc(NoAllocDevice* d, const void* q, const void* kc
   kern<<<grid, DEC_WARPS * 32, SMEM, st>>>((const bf16*)q, (const bf16*)kc, (const bf16*)vc,
                                            (const int*)bt, (const int*)lens, (bf16*)out, part_o,
                                            part_lse, nq, nkv, block_size, max_blocks, nsplit,
-                                           scale * 1.4426950408889634f, num_blocks, d->status);
+                                           scale * 1.4426950408889634f, num_blocks, d->status,
+                                           (int*)nullptr);
   int rc = check_launch("noalloc paged_decode");
   if (rc != GV_OK) return rc;
   if (nsplit > 1) {

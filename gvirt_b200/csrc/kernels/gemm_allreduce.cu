@@ -16,6 +16,12 @@
 // Tiles that finish early are already crossing NVSwitch while later tiles are still in their K
 // loop: the transfer overlaps the math tile by tile.
 //
+// With `residual` the reduced rows are added to the residual stream (`out` may be `residual`
+// itself), and with `ss_out` every rank also leaves the per-(tile, token) sums of squares of the
+// new rows behind: the consumer GEMM (gemm_decode.cu) turns them into the RMSNorm factor in its
+// epilogue, so the add + norm launch that follows o_proj / down_proj in the reference
+// (xlite/csrc/model.cpp:1413-1433) disappears under tensor parallelism as well.
+//
 // This replaces the reference's matmul followed by a separate `XliteOpAllReduceSum` launch after
 // o_proj / down_proj (xlite/csrc/model.cpp:583-594, 836-850; XCCL pull + bf16 atomic adds in
 // xlite/csrc/kernels/all_reduce.cpp:237-332).
@@ -44,6 +50,8 @@ struct ArArgs {
   unsigned int* state;    // local {generation, ticket}
   int rank, R, m_cap;
   int two_shot;           // 1: column c of tile t is reduced by rank (t + c) % R and broadcast
+  float* ss_out;          // [tokens][ss_ld]: entry [t][tile] = sum of squares of the finished row t in tile, or null
+  int ss_ld;
 };
 
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
@@ -85,6 +93,19 @@ __device__ __forceinline__ void add_bf2(float* acc, uint32_t packed) {
   acc[1] += __high2float(t);
 }
 
+// Sum of squares of the four bf16 values of a finished line, summed over the 32 lanes of the
+// warp (= the 128 features of the tile for one token column); lane 0 stores it. Every lane of the
+// warp must call it (the launcher requires N % 128 == 0 when `ss_out` is given).
+__device__ __forceinline__ void emit_sumsq(float* ss_out, int ss_ld, int tile, int c, uint32_t lo,
+                                           uint32_t hi) {
+  if (ss_out == nullptr) return;
+  float f[4] = {0.f, 0.f, 0.f, 0.f};
+  add_bf2(f, lo);
+  add_bf2(f + 2, hi);
+  const float ss = warp_sum(f[0] * f[0] + f[1] * f[1] + f[2] * f[2] + f[3] * f[3]);
+  if ((threadIdx.x & 31) == 0) ss_out[(long long)c * ss_ld + tile] = ss;
+}
+
 // Reduces this thread's share (entries `first`, `first + 4`, ... of the column list `cols[0..n)`)
 // of one 4-feature line: NSRC remote partials polled out of this rank's receive region plus its
 // own partial from `tile`, summed in rank order. RB rows are kept in flight at once so that the
@@ -93,12 +114,12 @@ __device__ __forceinline__ void add_bf2(float* acc, uint32_t packed) {
 // region, at byte offset bcast_off of its slab, line index c * lines_per_row + feat / 4.
 template <int NSRC, int BM_>
 __device__ __forceinline__ bool reduce_lines(const uint4* __restrict__ base, const bf16* tile,
-                                             bf16* __restrict__ out, const bf16* __restrict__ bias,
-                                             const bf16* __restrict__ residual, long long ldo,
+                                             bf16* out, const bf16* __restrict__ bias,
+                                             const bf16* residual, long long ldo,
                                              int rank, int m_cap, int lines_per_row, int feat,
                                              int line, int first, const short* cols, int n,
                                              uint32_t gen, void* const* bcast_peers,
-                                             long long bcast_off) {
+                                             long long bcast_off, float* ss_out, int ss_ld) {
   constexpr int R = NSRC + 1;
   constexpr int RB = 16 / NSRC > 0 ? 16 / NSRC : 1;
   bool ok = true;
@@ -159,6 +180,7 @@ __device__ __forceinline__ bool reduce_lines(const uint4* __restrict__ base, con
       o.x = pack2(acc[0], acc[1]);
       o.y = pack2(acc[2], acc[3]);
       *reinterpret_cast<uint2*>(out + (long long)c * ldo + feat) = o;
+      emit_sumsq(ss_out, ss_ld, blockIdx.x, c, o.x, o.y);
       if (bcast_peers != nullptr) {
 #pragma unroll
         for (int p = 1; p < R; ++p) {
@@ -175,9 +197,10 @@ __device__ __forceinline__ bool reduce_lines(const uint4* __restrict__ base, con
 
 // Two-shot, receiving side: wait for the owners' finished lines of the columns `cols[0..n)` in
 // this rank's final region and copy them to `out`. Up to 16 rows in flight.
-__device__ __forceinline__ bool copy_final_lines(const uint4* __restrict__ fin, bf16* __restrict__ out,
+__device__ __forceinline__ bool copy_final_lines(const uint4* __restrict__ fin, bf16* out,
                                                  long long ldo, int lines_per_row, int feat, int first,
-                                                 const short* cols, int n, uint32_t gen) {
+                                                 const short* cols, int n, uint32_t gen, float* ss_out,
+                                                 int ss_ld) {
   bool ok = true;
   for (int i0 = first; i0 < n; i0 += 4 * 16) {
     uint4 v[16];
@@ -193,6 +216,7 @@ __device__ __forceinline__ bool copy_final_lines(const uint4* __restrict__ fin, 
       const int c = cols[i];
       if (!wait_line(fin + (long long)c * lines_per_row + (feat >> 2), gen, v[rr], ok ? GV_WAIT_NS : 0ull)) ok = false;
       *reinterpret_cast<uint2*>(out + (long long)c * ldo + feat) = make_uint2(v[rr].x, v[rr].z);
+      emit_sumsq(ss_out, ss_ld, blockIdx.x, c, v[rr].x, v[rr].z);
     }
   }
   return ok;
@@ -201,9 +225,8 @@ __device__ __forceinline__ bool copy_final_lines(const uint4* __restrict__ fin, 
 template <int BN>
 __global__ void __launch_bounds__(NUM_THREADS, 2)
 gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
-                      bf16* __restrict__ out, const bf16* __restrict__ bias,
-                      const bf16* __restrict__ residual, int N, int M, int K, long long ldo,
-                      int splitk, ArArgs a, unsigned int* status) {
+                      bf16* out, const bf16* __restrict__ bias, const bf16* residual, int N, int M,
+                      int K, long long ldo, int splitk, ArArgs a, unsigned int* status) {
   using C = Cfg<BN, 108>;
   extern __shared__ uint8_t smem_raw[];
   const Shared sh = carve<C>(smem_raw);
@@ -320,7 +343,8 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
       void* const* bc = a.two_shot ? a.peers : nullptr;
 #define GV_AR_REDUCE(NSRC)                                                                        \
   ok = reduce_lines<NSRC, BM>(base, tile, out, bias, residual, ldo, a.rank, a.m_cap,              \
-                              lines_per_row, feat, line, rsub, s_own, nown, gen, bc, fin_off)
+                              lines_per_row, feat, line, rsub, s_own, nown, gen, bc, fin_off,    \
+                              a.ss_out, a.ss_ld)
       switch (a.R) {
         case 1: {  // single rank: own partial only
           for (int i = rsub; i < nown; i += 4) {
@@ -343,6 +367,7 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
             o.x = pack2(acc[0], acc[1]);
             o.y = pack2(acc[2], acc[3]);
             *reinterpret_cast<uint2*>(out + (long long)c * ldo + feat) = o;
+            emit_sumsq(a.ss_out, a.ss_ld, blockIdx.x, c, o.x, o.y);
           }
           break;
         }
@@ -359,7 +384,8 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
       // ---- two-shot: collect the finished lines of the columns other ranks own
       if (a.two_shot && noth > 0) {
         const uint4* fin = reinterpret_cast<const uint4*>(static_cast<char*>(a.peers[a.rank]) + fin_off);
-        if (!copy_final_lines(fin, out, ldo, lines_per_row, feat, rsub, s_oth, noth, gen)) ok = false;
+        if (!copy_final_lines(fin, out, ldo, lines_per_row, feat, rsub, s_oth, noth, gen, a.ss_out, a.ss_ld))
+          ok = false;
       }
       if (!ok) atomicOr(status, GV_ST_TIMEOUT_PEER);
     }
@@ -433,13 +459,15 @@ using namespace gv::gemm;
 // out [M, N] local. Receive region must hold 2 * (R + 1) * m_cap * N / 4 sixteen-byte lines
 // (= 8 * (R + 1) * m_cap * N bytes): per parity R partial regions, then (after all of them) one
 // final region per parity that only the two-shot mode uses. Returns GV_EUNSUPPORTED when the shape does not fit the fused path (caller falls back).
-extern "C" int gv_gemm_allreduce(const void* x, const void* w, const void* bias,
-                                 const void* residual, void* out, long long M, long long N,
-                                 long long K, long long ldx, long long ldw, long long ldo,
-                                 const void* peers, long long recv_off, long long flags_off,
-                                 void* state, long long rank, long long R, long long m_cap,
-                                 long long max_ctas, long long two_shot, void* stream) {
+extern "C" int gv_gemm_allreduce_ss(const void* x, const void* w, const void* bias,
+                                    const void* residual, void* out, void* ss_out, long long ss_ld,
+                                    long long M, long long N, long long K, long long ldx,
+                                    long long ldw, long long ldo, const void* peers,
+                                    long long recv_off, long long flags_off, void* state,
+                                    long long rank, long long R, long long m_cap,
+                                    long long max_ctas, long long two_shot, void* stream) {
   if (!x || !w || !out || !peers || !state || M <= 0 || N <= 0 || K <= 0) return GV_EINVAL;
+  if (ss_out && ((N % 128) || ss_ld < N / 128)) return GV_EINVAL;
   if ((K & 7) || (ldx & 7) || (ldw & 7) || (N & 7) || (ldo & 7)) return GV_EINVAL;
   if (M > 256 || M > m_cap || R < 1 || R > AR_MAX_RANKS) return GV_EUNSUPPORTED;
   const int tiles = ceil_div(N, BM);
@@ -468,6 +496,8 @@ extern "C" int gv_gemm_allreduce(const void* x, const void* w, const void* bias,
   a.R = (int)R;
   a.m_cap = (int)m_cap;
   a.two_shot = (two_shot && R > 1) ? 1 : 0;
+  a.ss_out = (float*)ss_out;
+  a.ss_ld = (int)ss_ld;
   cudaStream_t st = (cudaStream_t)stream;
   switch (bn) {
     case 16: return launch_ar<16>(tmW, tmX, (bf16*)out, (const bf16*)bias, (const bf16*)residual, (int)N, (int)M, (int)K, ldo, sk, a, st);
@@ -475,4 +505,14 @@ extern "C" int gv_gemm_allreduce(const void* x, const void* w, const void* bias,
     case 64: return launch_ar<64>(tmW, tmX, (bf16*)out, (const bf16*)bias, (const bf16*)residual, (int)N, (int)M, (int)K, ldo, sk, a, st);
     default: return launch_ar<128>(tmW, tmX, (bf16*)out, (const bf16*)bias, (const bf16*)residual, (int)N, (int)M, (int)K, ldo, sk, a, st);
   }
+}
+
+extern "C" int gv_gemm_allreduce(const void* x, const void* w, const void* bias,
+                                 const void* residual, void* out, long long M, long long N,
+                                 long long K, long long ldx, long long ldw, long long ldo,
+                                 const void* peers, long long recv_off, long long flags_off,
+                                 void* state, long long rank, long long R, long long m_cap,
+                                 long long max_ctas, long long two_shot, void* stream) {
+  return gv_gemm_allreduce_ss(x, w, bias, residual, out, nullptr, 0, M, N, K, ldx, ldw, ldo, peers,
+                              recv_off, flags_off, state, rank, R, m_cap, max_ctas, two_shot, stream);
 }

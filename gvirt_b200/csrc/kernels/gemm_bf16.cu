@@ -366,6 +366,20 @@ static int lookup_splitk(long long N, long long K, int bn) {
   return it == g_splitk_override.end() ? 0 : it->second;
 }
 
+// Cluster split-K factor of a weight-major launch over weights [N, K] with a `bn`-token tile:
+// `force` if positive, else the measured table, else the heuristic; clamped so that every split
+// owns at least one k-block. Shared with the fused decode GEMMs (gemm_decode.cu).
+int decode_splitk(long long N, long long K, int bn, long long force) {
+  const int tiles = ceil_div(N, BM);
+  const int kb_total = ceil_div(K, BK);
+  int sk = force > 0 ? (int)force : lookup_splitk(N, K, bn);
+  if (sk <= 0) sk = pick_splitk(tiles, kb_total, num_sms());
+  if (sk > 8) sk = 8;
+  if (sk > kb_total) sk = kb_total;
+  const int per = (kb_total + sk - 1) / sk;
+  return (kb_total + per - 1) / per;
+}
+
 }  // namespace gemm
 }  // namespace gv
 

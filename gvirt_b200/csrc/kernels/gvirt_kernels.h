@@ -79,6 +79,44 @@ int gv_paged_attention_prefill(const void* q, const void* k_cache, const void* v
                                long long head_dim, long long block_size, long long max_blocks,
                                float scale, long long num_blocks, void* stream);
 
+// In-kernel split merge (one launch): `counters` = batch * nkv int32, zero before the first call.
+int gv_paged_attention_decode_merged(const void* q, const void* k_cache, const void* v_cache,
+                                     const void* block_tables, const void* seq_lens, void* out,
+                                     void* part_o, void* part_lse, void* counters, long long batch,
+                                     long long nq, long long nkv, long long head_dim,
+                                     long long block_size, long long max_blocks, long long nsplit,
+                                     float scale, long long num_blocks, void* stream);
+// tcgen05 / TMEM / TMA flash attention for head_dim 128 (attention_prefill_tc.cu).
+int gv_paged_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache,
+                                  const void* block_tables, const void* q_start,
+                                  const void* cached_lens, void* out, long long total_tokens,
+                                  long long batch, long long max_q_len, long long nq, long long nkv,
+                                  long long head_dim, long long block_size, long long max_blocks,
+                                  float scale, long long num_blocks, void* stream);
+
+// ---- decode-step GEMMs with fused epilogues (gemm_decode.cu)
+int gv_gemm_decode(const void* x, const void* w, const void* bias, void* out, long long M, long long N,
+                   long long K, long long ldx, long long ldw, long long ldo, const void* ss_in,
+                   long long ss_tiles, long long ss_ld, long long norm_h, float eps, long long swiglu,
+                   long long force_splitk, void* stream);
+int gv_gemm_decode_residual(const void* x, const void* w, const void* bias, const void* residual,
+                            void* x_out, void* ss_out, long long M, long long N, long long K,
+                            long long ldx, long long ldw, long long ldo, long long ss_ld,
+                            long long force_splitk, void* stream);
+int gv_gemm_decode_rope(const void* x, const void* w, const void* bias, void* q_out, void* k_cache,
+                        void* v_cache, const void* cos_sin, const void* positions, const void* slots,
+                        const void* q_norm_w, const void* k_norm_w, long long M, long long K,
+                        long long ldx, long long ldw, long long nq, long long nkv, float q_scale,
+                        float qk_eps, long long max_pos, long long num_slots, const void* ss_in,
+                        long long ss_tiles, long long ss_ld, long long norm_h, float eps,
+                        long long force_splitk, void* stream);
+int gv_gemm_allreduce_ss(const void* x, const void* w, const void* bias, const void* residual, void* out,
+                         void* ss_out, long long ss_ld, long long M, long long N, long long K,
+                         long long ldx, long long ldw, long long ldo, const void* peers,
+                         long long recv_off, long long flags_off, void* state, long long rank,
+                         long long R, long long m_cap, long long max_ctas, long long two_shot,
+                         void* stream);
+
 // ---- sampling
 int gv_sample(const void* logits, long long is_f32, long long ld, long long batch, long long vocab,
               const void* temperature, const void* top_k, const void* top_p, long long seed,

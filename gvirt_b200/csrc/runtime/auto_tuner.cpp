@@ -13,8 +13,21 @@ SplitChoice pick_decode_splits(int batch, int kv_heads, int max_kv_len, int num_
   SplitChoice best{1, std::max(kWarpTile, (max_kv_len + kWarpTile - 1) / kWarpTile * kWarpTile), -1.0};
   if (batch <= 0 || kv_heads <= 0 || max_kv_len <= 0) return best;
   const int slots = std::max(1, num_sms * std::max(1, ctas_per_sm));
-  const int limit = std::max(1, std::min(max_splits, (max_kv_len + kMinChunk - 1) / kMinChunk));
-  for (int s = 1; s <= limit; ++s) {
+  int limit = std::max(1, std::min(max_splits, (max_kv_len + kMinChunk - 1) / kMinChunk));
+  // Measured on B200 (64 requests, context 1060 - 1168, 128-wide heads): once the unsplit grid has
+  // about two thirds of an SM count of tasks, every split costs more in partial writes and merge
+  // work than it wins in balance (512 tasks: 51 us unsplit, 78 us with 2 splits; 128 tasks: 20.5
+  // against 24.0), while 64 tasks do gain from 4 splits (20.0 -> 17.2 us). So such grids stay
+  // unsplit, and the others get at most enough splits for about 1.75 tasks per SM.
+  const long long base_tasks = (long long)batch * kv_heads;
+  int lowest = 1;
+  if (base_tasks * 3 >= (long long)num_sms * 2) {
+    limit = 1;
+  } else {
+    limit = (int)std::max<long long>(1, std::min<long long>(limit, (long long)num_sms * 7 / 4 / base_tasks));
+    lowest = limit;                       // small grids: fill the device (about 1.75 tasks per SM)
+  }
+  for (int s = lowest; s <= limit; ++s) {
     int chunk = (max_kv_len + s - 1) / s;
     chunk = (chunk + kWarpTile - 1) / kWarpTile * kWarpTile;
     if ((long long)chunk * (s - 1) >= max_kv_len && s > 1) continue;  // last split would be empty

@@ -436,6 +436,9 @@ def save_hf_checkpoint(cfg: ModelConfig, weights: SimpleNamespace, path: str, sh
 
     def save_layer(i, L, moe):
         p = f"model.layers.{i}."
+        if getattr(L, "norm_folded", False):    # norm weights folded into w_qkv / w_gate_up: undo
+            from ..ops.decode_ops import unfolded_layer
+            L = unfolded_layer(L)
         t[p + "input_layernorm.weight"] = nrm(L.attn_norm)
         t[p + "post_attention_layernorm.weight"] = nrm(L.mlp_norm)
         a = p + "self_attn."

@@ -19,6 +19,7 @@ import torch
 
 from ..config import AttnType, ModelConfig, flags
 from ..engine.arena import TorchWorkspace, Workspace
+from ..ops import decode_ops as D
 from ..ops import functional as F
 from ..ops import reference as ref
 from ..parallel import collectives as coll
@@ -53,6 +54,8 @@ class Transformer:
         if cfg.mrope_sections is not None:
             self.mrope_mode = 2 if cfg.mrope_interleaved else 1
         self.debug_hook = None  # callable(tag, layer, tensor) for layer-level A/B diffing
+        self.fused_decode = False   # set by _fold_norms: steps of <= 128 tokens take _forward_decode_fused
+        self.rope_fused = False
         self._prepare_device_layouts()
 
     def _prepare_device_layouts(self, force: bool = False) -> None:
@@ -80,6 +83,28 @@ class Transformer:
                 w, lw.w_down, lw.gu_pad = F.pad_gate_up_down(w, wd, 64)
             lw.w_gate_up = F.interleave_gate_up(w)
             lw.gu_il = True
+        self._fold_norms()
+
+    def _fold_norms(self) -> None:
+        """Dense RMSNorm + MHA models: fold each layer's norm weights into w_qkv / w_gate_up so that
+        steps of up to 128 tokens can run without norm launches (``_forward_decode_fused``). Every
+        other path keeps working on the folded weights because the norm weights become ones."""
+        cfg = self.cfg
+        self.fused_decode = False
+        if not flags().fused_decode or cfg.attn_type != AttnType.MHA or cfg.is_moe or cfg.qk_norm_full:
+            return
+        if cfg.attn_output_gate or any(cfg.layer_is_linear_attn(i) for i in range(cfg.num_layers)):
+            return
+        if cfg.hidden_size % 128 or any(getattr(lw, "norm_folded", False) for lw in self.w.layers):
+            return
+        for lw in self.w.layers:
+            if (not getattr(lw, "gu_il", False) or lw.w_qkv.dtype != self.dtype or lw.w_o.dtype != self.dtype
+                    or lw.w_down.dtype != self.dtype or lw.w_o.shape[0] % 128):
+                return
+        for lw in self.w.layers:
+            D.fold_layer_norms(lw)
+        self.fused_decode = True
+        self.rope_fused = D.rope_fusable(cfg, self.hd, self.mrope_mode)
 
     # ------------------------------------------------------------------ KV cache
     def kv_cache_shapes(self, num_blocks: int) -> List[Tuple[Tuple[int, ...], ...]]:
@@ -179,6 +204,75 @@ class Transformer:
         ws.put(a)
         return out
 
+    # ------------------------------------------------------------------ fused decode forward
+    def _residual_linear(self, a, w, x, ss, ws) -> int:
+        """x += all_reduce_tp(a @ w^T) in place with the sums of squares of the new rows in `ss`.
+        Returns how many tiles of `ss` are valid (all of them from a fused producer, one from the
+        stand-alone add)."""
+        ctx = self.ctx
+        tiles = w.shape[0] // 128
+        if ctx.tp == 1:
+            D.linear_residual(a, w, x, ss)
+            return tiles
+        if a.device.type == "meta":
+            tmp = ws.get(tuple(x.shape), self.dtype)       # the unfused fall-back sizes the arena
+            ws.put(tmp)
+            return tiles
+        heap = ctx.symm
+        if heap is not None and a.is_cuda and heap.can_fuse_gemm_ar(a, w):
+            heap.gemm_allreduce(a, w, out=x, residual=x, ss_out=ss)
+            return tiles
+        tmp = ws.get(tuple(x.shape), self.dtype)
+        F.linear(a, w, None, out=tmp)
+        coll.all_reduce(tmp, ctx.tp_group, ctx)
+        D.add_residual_sumsq(tmp, x, ss)
+        ws.put(tmp)
+        return 1
+
+    def _forward_decode_fused(self, tokens, meta, kv_caches, ws):
+        """Layer loop for steps of up to 128 tokens of a dense model with folded norm weights: five
+        launches per layer (QKV GEMM with RoPE + cache write, attention, o_proj, gate/up GEMM with
+        SwiGLU, down_proj) against the nine of the generic loop. The residual stream `x` is updated
+        in place by the o_proj / down_proj epilogues (under tensor parallelism: by the reduce phase
+        of the fused GEMM + all-reduce), which also leave the sums of squares that the next GEMM
+        turns into the RMSNorm factor."""
+        cfg = self.cfg
+        T = tokens.shape[0]
+        H, eps = cfg.hidden_size, cfg.rms_norm_eps
+        nq, nkv, hd = self.nq, self.nkv, self.hd
+        x = self._embed(tokens, ws)
+        ss = ws.get((D.MAX_TOKENS, H // 128), torch.float32)
+        D.row_sumsq(x, ss)
+        nt = 1
+        for li, lw in enumerate(self.w.layers):
+            cache = kv_caches[li]
+            q = ws.get((T, nq * hd), self.dtype)
+            qk_nw = (lw.q_norm, lw.k_norm) if cfg.qk_norm else (None, None)
+            if self.rope_fused:
+                D.linear_rope(x, lw.w_qkv, meta, self.cos_sin, cache[0], cache[1], nq, nkv, ss, H, eps,
+                              bias=lw.b_qkv, q_norm_w=qk_nw[0], k_norm_w=qk_nw[1], qk_eps=eps, tiles=nt, out=q)
+            else:
+                qkv = ws.get((T, (nq + 2 * nkv) * hd), self.dtype)
+                D.linear_scaled(x, lw.w_qkv, ss, H, eps, tiles=nt, out=qkv)
+                F.rope_kvwrite(qkv, meta, self.cos_sin, cache[0], cache[1], nq, nkv, hd, cfg.rot_dim, hd ** -0.5,
+                               lw.b_qkv, qk_nw[0], qk_nw[1], eps, self.mrope_mode, cfg.mrope_sections or (0, 0, 0),
+                               cfg.rope_interleaved, out=q)
+                ws.put(qkv)
+            o = ws.get((T, nq * hd), self.dtype)
+            F.paged_attention(q, cache[0], cache[1], meta, nq, nkv, hd, 1.0, out=o)
+            ws.put(q)
+            nt = self._residual_linear(o, lw.w_o, x, ss, ws)
+            ws.put(o)
+            a = ws.get((T, lw.w_gate_up.shape[0] // 2), self.dtype)
+            D.linear_scaled(x, lw.w_gate_up, ss, H, eps, swiglu=True, tiles=nt, out=a)
+            nt = self._residual_linear(a, lw.w_down, x, ss, ws)
+            ws.put(a)
+        ws.put(ss)
+        h = ws.get((T, H), self.dtype)
+        F.rmsnorm(x, self.w.final_norm, eps, out=h)
+        ws.put(x)
+        return h
+
     # ------------------------------------------------------------------ sequence-parallel forward
     def _use_sp(self, T: int) -> bool:
         cfg, ctx = self.cfg, self.ctx
@@ -274,8 +368,11 @@ class Transformer:
         cfg = self.cfg
         ws = ws or TorchWorkspace(self.device)
         T = tokens.shape[0] if inputs_embeds is None else inputs_embeds.shape[0]
-        if (allow_sp and inputs_embeds is None and deepstack is None and mm_override is None
-                and self._use_sp(T)):
+        plain = inputs_embeds is None and deepstack is None and mm_override is None
+        if (plain and self.fused_decode and 0 < T <= D.MAX_TOKENS
+                and self.debug_hook is None):
+            return self._forward_decode_fused(tokens, meta, kv_caches, ws)
+        if allow_sp and plain and self._use_sp(T):
             return self._forward_sp(tokens, meta, kv_caches, ws)
         if inputs_embeds is not None:
             x = ws.get((T, cfg.hidden_size), self.dtype)

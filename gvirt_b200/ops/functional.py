@@ -248,6 +248,19 @@ def rope_kvwrite(qkv, meta: AttnMeta, cos_sin, k_cache, v_cache, nq, nkv, hd, ro
 
 
 # --------------------------------------------------------------------------- paged attention
+_COUNTERS: dict = {}
+
+
+def _decode_counters(device, n: int) -> torch.Tensor:
+    """Zeroed int32 ticket counters for the in-kernel split merge, one array per (device, stream):
+    the kernel returns them to zero, so calls ordered on one stream share the array."""
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    t = _COUNTERS.get(key)
+    if t is None or t.numel() < n:
+        t = _COUNTERS[key] = torch.zeros(max(n, 4096), dtype=torch.int32, device=device)
+    return t
+
+
 @_dry
 def paged_attention(q, k_cache, v_cache, meta: AttnMeta, nq, nkv, hd, scale=1.0, out=None):
     """Causal GQA attention over the paged KV cache. q [T, nq*hd] pre-scaled."""
@@ -276,9 +289,17 @@ def paged_attention(q, k_cache, v_cache, meta: AttnMeta, nq, nkv, hd, scale=1.0,
             else:
                 po, pl = meta.split_scratch
                 assert po.numel() >= T * nq * ns * hd and pl.numel() >= T * nq * ns
-        _native.call("paged_attention_decode", q, k_cache, v_cache, meta.block_tables, meta.seq_lens,
-                     out, po, pl, T, nq, nkv, hd, meta.block_size, max_blocks, ns, float(scale),
-                     num_blocks)
+        # the CTA that finishes a (request, kv head) last merges its splits: one launch
+        cnt = _decode_counters(q.device, T * nkv) if ns > 1 else None
+        _native.call("paged_attention_decode_merged", q, k_cache, v_cache, meta.block_tables,
+                     meta.seq_lens, out, po, pl, cnt, T, nq, nkv, hd, meta.block_size, max_blocks, ns,
+                     float(scale), num_blocks)
+    elif (hd == 128 and _flags().prefill_attn_tc and meta.block_size >= 8
+          and meta.block_size & (meta.block_size - 1) == 0 and q.is_contiguous() and out.is_contiguous()):
+        # tcgen05 / TMEM / TMA flash attention (attention_prefill_tc.cu)
+        _native.call("paged_attention_prefill_tc", q, k_cache, v_cache, meta.block_tables,
+                     meta.query_start_loc, meta.cached_lens, out, T, meta.batch, meta.max_q_len, nq,
+                     nkv, hd, meta.block_size, max_blocks, float(scale), num_blocks)
     else:
         _native.call("paged_attention_prefill", q, k_cache, v_cache, meta.block_tables,
                      meta.query_start_loc, meta.cached_lens, out, meta.batch, meta.max_q_len, nq,
