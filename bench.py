@@ -173,8 +173,15 @@ def main():
     runner = llm.runner
     build_s = time.perf_counter() - t_build
 
+    # ---- warm-up of the prefill path: one untimed chunk-sized batch of requests, so that one-off
+    # costs (communicator set-up of the first large collective, tensor-map encoding, kernel
+    # attributes) are not billed to the first requests' time to first token
+    g = torch.Generator().manual_seed(99 + ctx.dp_rank)
+    n_warm = max(1, min(B, args.max_tokens // P))
+    warm = torch.randint(0, cfg.vocab_size, (n_warm, P), generator=g).tolist()
+    llm.generate(warm, SamplingParams(max_tokens=2, ignore_eos=True))
+    torch.cuda.synchronize()
     # ---- prefill all requests through the engine (chunked), then warm-up decode steps
-    g = torch.Generator().manual_seed(1234)
     g.manual_seed(1234 + ctx.dp_rank)
     prompts = torch.randint(0, cfg.vocab_size, (B, P), generator=g).tolist()
     sp = SamplingParams(max_tokens=2 * total_new + 8, ignore_eos=True)

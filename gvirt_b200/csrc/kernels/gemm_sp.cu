@@ -39,6 +39,7 @@ int cached_tmap_bf16(CUtensorMap* out, const void* base, long long rows, long lo
 
 constexpr int SP_BN = 128;
 constexpr int SP_MAX_RANKS = 16;
+constexpr int SP_RS_MAX_RANKS = 8;   // ranks the reduce phase of gemm_rs unrolls over
 
 __device__ __forceinline__ void sp_epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 __device__ __forceinline__ uint4 sp_ld_sys16(const void* p) {
@@ -127,19 +128,30 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         sm100::tmem_ld16(tmem_addr(tmem_base, quad, c), r);
         sm100::tmem_ld_wait();
         if (n0 + c + 16 > N) continue;
+        // all remote partials of this chunk are requested before any is consumed: up to
+        // 2 (R - 1) independent 16-byte loads in flight per thread instead of a chain of them
+        uint4 v[SP_RS_MAX_RANKS][2];
+#pragma unroll
+        for (int s = 0; s < SP_RS_MAX_RANKS; ++s) {
+          if (s < a.R && s != a.rank) {
+            const bf16* src = base + ((long long)s * a.m_r_cap + row) * N + n0 + c;
+            v[s][0] = sp_ld_sys16(src);
+            v[s][1] = sp_ld_sys16(src + 8);
+          }
+        }
         float acc[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) acc[j] = 0.f;
-        for (int s = 0; s < a.R; ++s) {  // rank order; this rank's own partial is the accumulator
+#pragma unroll
+        for (int s = 0; s < SP_RS_MAX_RANKS; ++s) {  // rank order; this rank's own partial is the accumulator
+          if (s >= a.R) continue;
           if (s == a.rank) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) acc[j] += bf2f(f2bf(__uint_as_float(r[j])));
           } else {
-            const bf16* src = base + ((long long)s * a.m_r_cap + row) * N + n0 + c;
-            const uint4 v0 = sp_ld_sys16(src), v1 = sp_ld_sys16(src + 8);
             float f[16];
-            unpack8(*reinterpret_cast<const bf16x8*>(&v0), f);
-            unpack8(*reinterpret_cast<const bf16x8*>(&v1), f + 8);
+            unpack8(*reinterpret_cast<const bf16x8*>(&v[s][0]), f);
+            unpack8(*reinterpret_cast<const bf16x8*>(&v[s][1]), f + 8);
 #pragma unroll
             for (int j = 0; j < 16; ++j) acc[j] += f[j];
           }
@@ -291,7 +303,7 @@ extern "C" int gv_gemm_rs(const void* x, const void* w, void* out, long long M, 
                           long long rank, long long R, long long m_r_cap, void* stream) {
   if (!x || !w || !out || !peers || !state) return GV_EINVAL;
   if (M <= 0 || M % (BM * R) || (N & 15) || (K & 7) || (ldx & 7) || (ldw & 7) || (ldo & 7)) return GV_EINVAL;
-  if (M / R > m_r_cap || R > SP_MAX_RANKS) return GV_ETOOBIG;
+  if (M / R > m_r_cap || R > SP_RS_MAX_RANKS) return GV_ETOOBIG;
   if ((long long)R * m_r_cap * N * 2 > recv_stride) return GV_ETOOBIG;
   using C = Cfg<SP_BN, 220>;
   if (!g_rs_conf) {

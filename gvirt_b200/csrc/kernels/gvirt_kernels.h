@@ -171,6 +171,11 @@ int gv_mla_attention(const void* qf, const void* cache, const void* block_tables
                      long long batch, long long heads, long long dc, long long dr,
                      long long block_size, long long max_blocks, long long nsplit, float scale,
                      long long num_blocks, const void* topk_idx, long long topk, void* stream);
+// Decode-only absorbed MLA on tcgen05 (mla_tc.cu): heads % 128 == 0, dc 512, dr 64, block_size % 32 == 0.
+int gv_mla_attention_tc(const void* qf, const void* cache, const void* block_tables, const void* seq_lens,
+                        void* out, void* part_o, void* part_lse, long long batch, long long heads,
+                        long long dc, long long dr, long long block_size, long long max_blocks,
+                        long long nsplit, float scale, long long num_blocks, void* stream);
 int gv_bmm_bf16(const void* x, const void* w, void* out, long long T, long long Hh, long long N,
                 long long K, long long sx_t, long long sx_h, long long so_t, long long so_h,
                 void* stream);

@@ -127,6 +127,12 @@ def mla_attention(qf, kv_cache, meta, hl, dc, dr, scale, out=None, topk_idx=None
     if ns > 1:
         po = torch.empty(T * hl * ns * dc, dtype=torch.float32, device=qf.device)
         pl = torch.empty(T * hl * ns, dtype=torch.float32, device=qf.device)
+    if (meta.decode_step and topk_idx is None and dc == 512 and dr == 64 and hl % 128 == 0
+            and meta.block_size % 32 == 0 and F._flags().mla_attn_tc and qf.is_contiguous() and out.is_contiguous()):
+        # tcgen05 / TMEM / TMA kernel: the 128 heads of a request on the TMEM lanes (mla_tc.cu)
+        _native.call("mla_attention_tc", qf, kv_cache, meta.block_tables, meta.seq_lens, out, po, pl, T, hl, dc, dr,
+                     meta.block_size, meta.block_tables.shape[1], ns, float(scale), kv_cache.shape[0])
+        return out
     _native.call("mla_attention", qf, kv_cache, meta.block_tables, meta.query_start_loc,
                  meta.cached_lens, out, po, pl, T, meta.batch, hl, dc, dr, meta.block_size,
                  meta.block_tables.shape[1], ns, float(scale), kv_cache.shape[0],

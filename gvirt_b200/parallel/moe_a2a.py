@@ -24,7 +24,11 @@ def a2a_capacity(cfg, R: int, tokens_cap: int) -> int:
     (R * tokens_cap); GVIRT_ACTIVE_TOKENS_RATIO_PER_EP scales it down, never below four times the
     expected load. Because the buffers between the two expert GEMMs are addressed by slot, their
     size follows this capacity too: it is cut further when they would exceed
-    GVIRT_A2A_SCRATCH_GB. Rows beyond the capacity are dropped and counted (status word)."""
+    GVIRT_A2A_SCRATCH_GB. With the default ratio of 1 nothing is ever dropped: where memory cuts
+    the capacity, `attach_device_comm` lowers the step size (`max_num_batched_tokens`) to
+    `a2a_exact_tokens`, so that even the worst routing fits. A ratio below 1 is the reference's
+    approximate mode (its ACTIVE_TOKENS_RATIO knob): rows beyond the capacity are dropped and
+    counted in the status word."""
     E = max(cfg.num_experts, 1)
     worst = R * tokens_cap
     expect = R * tokens_cap * cfg.num_experts_per_tok / E
@@ -38,6 +42,12 @@ def a2a_capacity(cfg, R: int, tokens_cap: int) -> int:
     if cap > fit:
         cap = max(floor, fit)
     return int(min(worst, cap))
+
+
+def a2a_exact_tokens(cfg, R: int, tokens_cap: int) -> int:
+    """Most tokens one rank may dispatch per step such that no routing whatsoever can overflow an
+    expert's receive region (every token of every rank to the same expert: R * tokens slots)."""
+    return min(int(tokens_cap), a2a_capacity(cfg, R, tokens_cap) // max(R, 1))
 
 
 class MoEA2A:
@@ -79,6 +89,16 @@ class MoEA2A:
         self.rows = rows
         self.row_of = torch.empty(self.tokens_cap, self.K, dtype=torch.int32, device=dev)
         self.avg_rows = max(1, int(expect + 0.5))
+        self._scratch: dict = {}       # buffers between the two expert GEMMs, shared by all layers
+
+    def _buf(self, name: str, shape, dtype) -> torch.Tensor:
+        """Slot-addressed intermediate of fixed worst-case size: allocated once (all layers run one
+        after the other on one stream), so a step allocates nothing."""
+        key = (name, tuple(shape), dtype)
+        t = self._scratch.get(key)
+        if t is None:
+            t = self._scratch[key] = torch.empty(tuple(shape), dtype=dtype, device=self.heap.device)
+        return t
 
     def supports(self, T: int) -> bool:
         return T <= self.tokens_cap
@@ -98,7 +118,7 @@ class MoEA2A:
         # the other ranks run a similar step): decode steps get narrow tiles, so the padding rows of
         # the activation tile do not double the bytes streamed next to the weights
         avg_rows = max(1, int(self.R * max(T, 1) * self.K / max(self.cfg.num_experts, 1) + 0.5))
-        gu = torch.empty(rows, 2 * inter, dtype=torch.bfloat16, device=dev)
+        gu = self._buf("gu", (rows, 2 * inter), torch.bfloat16)
         w13s, w2s = getattr(lw, "w13_scale", None), getattr(lw, "w2_scale", None)
         if self.fp8:
             _native.call("grouped_gemm_fp8_seg", self.xs, self.xscale, lw.w13, w13s, self.seg_start, self.seg_end,
@@ -106,23 +126,23 @@ class MoEA2A:
         else:
             _native.call("grouped_gemm_bf16_seg", self.xs, lw.w13, self.seg_start, self.seg_end, gu, rows,
                          2 * inter, self.H, E, E, avg_rows)
-        ys = torch.empty(rows, self.H, dtype=torch.bfloat16, device=dev)
+        ys = self._buf("ys", (rows, self.H), torch.bfloat16)
         # SwiGLU (and, for fp8 experts, the activation quantisation) over the live rows only
         seg_ok = inter % 128 == 0 and E <= 512
         if self.fp8:
             if seg_ok:
-                aq = torch.empty(rows, inter, dtype=torch.float8_e4m3fn, device=dev)
-                asc = torch.empty(inter // 128, rows, dtype=torch.float32, device=dev)
+                aq = self._buf("aq", (rows, inter), torch.float8_e4m3fn)
+                asc = self._buf("asc", (inter // 128, rows), torch.float32)
                 _native.call("moe_act_seg", gu, None, aq, asc, self.seg_start, self.seg_end, E, inter,
                              gu.stride(0), rows, float(clamp), 1)
             else:
-                act = torch.empty(rows, inter, dtype=torch.bfloat16, device=dev)
+                act = self._buf("act", (rows, inter), torch.bfloat16)
                 F.silu_and_mul(gu, out=act, clamp=clamp)
                 aq, asc = moe_ops.quant_fp8(act)
             _native.call("grouped_gemm_fp8_seg", aq, asc, lw.w2, w2s, self.seg_start, self.seg_end, ys, rows,
                          self.H, inter, E, E, asc.shape[1], avg_rows)
         else:
-            act = torch.empty(rows, inter, dtype=torch.bfloat16, device=dev)
+            act = self._buf("act", (rows, inter), torch.bfloat16)
             if seg_ok:
                 _native.call("moe_act_seg", gu, act, None, None, self.seg_start, self.seg_end, E, inter,
                              gu.stride(0), rows, float(clamp), 0)

@@ -7,6 +7,7 @@
     python -m gvirt_b200.tools.kbench layer --tp 1            # one Llama-3-8B decode layer, by parts
     python -m gvirt_b200.tools.kbench prefill_gemm --m 8192   # token-major / persistent kernels / cuBLAS
     python -m gvirt_b200.tools.kbench rope --tokens 8192      # RoPE + cache write on a prefill chunk
+    python -m gvirt_b200.tools.kbench prefill_attn --batch 8 --tokens 1024   # tcgen05 vs mma.sync prefill attention
 
 Each case runs `--chain` calls with rotating operands (so that nothing is served from L2) inside
 one CUDA graph, times `--reps` replays with CUDA events after warm-up and prints one JSON line
@@ -295,9 +296,34 @@ def case_rope(args):
     _report("rope", us, nbytes, args, tokens=T, generic_kernel=bool(os.environ.get("GVIRT_DISABLE_ROPE_FAST")))
 
 
+def case_prefill_attn(args):
+    """Causal prefill attention over `--batch` requests of `--tokens` new tokens each (no cached
+    prefix), 128-wide heads: the tcgen05 kernel against the mma.sync kernel, TFLOP/s counted as
+    4 * tokens^2 / 2 * head_dim per (request, head) (the causal half)."""
+    dev = "cuda"
+    B, S, nq, nkv, hd, bs = args.batch, args.tokens, args.nq, args.nkv, 128, 128
+    nblk = (S + bs - 1) // bs
+    bt = torch.randperm(B * nblk, device=dev).view(B, nblk).int()
+    qsl = (torch.arange(B + 1, device=dev) * S).int()
+    cached = torch.zeros(B, dtype=torch.int32, device=dev)
+    kc = (torch.randn(B * nblk, bs, nkv, hd, device=dev) * 0.5).bfloat16()
+    vc = (torch.randn(B * nblk, bs, nkv, hd, device=dev) * 0.5).bfloat16()
+    q = (torch.randn(B * S, nq * hd, device=dev) * 0.3).bfloat16()
+    o1, o2 = torch.empty_like(q), torch.empty_like(q)
+    flops = 4.0 * B * nq * hd * S * (S + 1) / 2
+    t_tc = _plain_us(lambda: _native.call("paged_attention_prefill_tc", q, kc, vc, bt, qsl, cached, o1, B * S, B, S,
+                                          nq, nkv, hd, bs, nblk, 1.0, B * nblk))
+    t_old = _plain_us(lambda: _native.call("paged_attention_prefill", q, kc, vc, bt, qsl, cached, o2, B, S, nq, nkv,
+                                           hd, bs, nblk, 1.0, B * nblk))
+    print(json.dumps({"case": "prefill_attn", "batch": B, "tokens": S, "nq": nq, "nkv": nkv,
+                      "tcgen05": {"us": round(t_tc, 1), "tflops": round(flops / t_tc / 1e6, 1)},
+                      "mma_sync": {"us": round(t_old, 1), "tflops": round(flops / t_old / 1e6, 1)},
+                      "maxdiff": (o1.float() - o2.float()).abs().max().item()}), flush=True)
+
+
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("case", choices=["gemm", "swiglu", "attn", "mla", "layer", "prefill_gemm", "rope"])
+    ap.add_argument("case", choices=["gemm", "swiglu", "attn", "mla", "layer", "prefill_gemm", "rope", "prefill_attn"])
     ap.add_argument("--tokens", type=int, default=8192)
     ap.add_argument("--with-persistent", action="store_true",
                     help="prefill_gemm: also time gemm_persist.cu (GVIRT_PREFILL_GEMM_PERSISTENT=2)")
@@ -321,7 +347,8 @@ def main() -> int:
         raise SystemExit("kbench needs a CUDA device")
     torch.manual_seed(0)
     {"gemm": case_gemm, "swiglu": lambda a: case_gemm(a, True), "attn": case_attn, "mla": case_mla,
-     "layer": case_layer, "prefill_gemm": case_prefill_gemm, "rope": case_rope}[args.case](args)
+     "layer": case_layer, "prefill_gemm": case_prefill_gemm, "rope": case_rope,
+     "prefill_attn": case_prefill_attn}[args.case](args)
     st = _native.read_status()
     if st:
         print(json.dumps({"status_word": st, "meaning": _native.describe_status(st)}))

@@ -115,3 +115,59 @@ def test_absorb_and_unabsorb_paths():
     mla_ops.unabsorb_o(oa.cuda(), w_uv.cuda(), out=got2)
     close(got2, want2, atol=3e-2, rtol=2e-2, what="unabsorb_o")
     status_ok()
+
+
+@pytest.mark.parametrize("ctx", [33000, 131071])
+def test_mla_decode_long_caches(ctx):
+    """The long end of the reference's sweep (xlite/tests/kernels/mla.py:61-76): 128 heads over one
+    long and one short cache, split-KV with the number of splits a serving step would pick."""
+    heads, dc, dr, bs = 128, 512, 64, 64
+    lens, cached = [1, 1], [ctx - 1, 700]
+    mc, m = _meta_for(lens, cached, bs, dc + dr)
+    m.decode_step = True
+    m.num_splits = 16
+    g = torch.Generator().manual_seed(ctx % 89)
+    nblk = int(mc.block_tables.max()) + 1
+    cache = (torch.randn(nblk, bs, 1, dc + dr, generator=g) * 0.5).bfloat16()
+    qf = (torch.randn(2, heads, dc + dr, generator=g) * 0.3).bfloat16()
+    scale = (dc + dr) ** -0.5
+    want = torch.zeros(2, heads, dc, dtype=torch.bfloat16)
+    mla_ops.mla_attention(qf, cache, mc, heads, dc, dr, scale, out=want)
+    got = torch.zeros(2, heads, dc, device=DEV, dtype=torch.bfloat16)
+    mla_ops.mla_attention(qf.to(DEV), cache.to(DEV), m, heads, dc, dr, scale, out=got)
+    close(got, want, atol=1e-2, rtol=3e-2, what=f"mla decode over {ctx} cached tokens")
+    status_ok()
+
+
+def test_mla_tc_rescales_its_output_when_the_maximum_climbs():
+    """Scores that grow along the sequence force the lazily moved maximum (and with it the
+    accumulated output in tensor memory) to be rescaled many times; padding rows give zeros."""
+    heads, dc, dr, bs = 128, 512, 64, 64
+    lens, cached = [1, 1, 1], [900, 0, 300]
+    mc, m = _meta_for(lens, cached, bs, dc + dr)
+    m.decode_step = True
+    g = torch.Generator().manual_seed(4)
+    nblk = int(mc.block_tables.max()) + 1
+    cache = (torch.randn(nblk, bs, 1, dc + dr, generator=g) * 0.5).bfloat16()
+    for b in range(3):
+        total = cached[b] + 1
+        for j in range((total + bs - 1) // bs):
+            blk = int(mc.block_tables[b, j])
+            pos = torch.arange(j * bs, (j + 1) * bs).float()
+            cache[blk] = (cache[blk].float() * (0.3 + pos / 60.0)[:, None, None]).bfloat16()
+    qf = (torch.randn(3, heads, dc + dr, generator=g) * 0.6).bfloat16()
+    scale = 0.3
+    want = torch.zeros(3, heads, dc, dtype=torch.bfloat16)
+    mla_ops.mla_attention(qf, cache, mc, heads, dc, dr, scale, out=want)
+    for ns in (1, 2):
+        m.num_splits = ns
+        got = torch.full((3, heads, dc), 7.0, device=DEV, dtype=torch.bfloat16)
+        mla_ops.mla_attention(qf.to(DEV), cache.to(DEV), m, heads, dc, dr, scale, out=got)
+        close(got, want, atol=2e-2, rtol=3e-2, what=f"mla tc with rescaling, {ns} split(s)")
+    m.seq_lens[1] = 0              # a padding row: zeros, nothing read
+    m.num_splits = 1
+    got = torch.full((3, heads, dc), 7.0, device=DEV, dtype=torch.bfloat16)
+    mla_ops.mla_attention(qf.to(DEV), cache.to(DEV), m, heads, dc, dr, scale, out=got)
+    assert (got[1] == 0).all()
+    close(got[0], want[0], atol=2e-2, rtol=3e-2, what="row beside a padding row")
+    status_ok()

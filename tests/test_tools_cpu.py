@@ -428,3 +428,37 @@ def test_causal_softmax_definition_matches_softmax_over_padded_rows():
     assert torch.equal(ref.causal_softmax(torch.randn(1, 16), 0), torch.zeros(1, 16))
     meta = torch.empty(2, 16, device="meta")
     assert F.softmax(meta, 3) is meta
+
+
+def test_moe_exchange_step_size_keeps_the_exchange_exact(monkeypatch):
+    """With the default ratio the fused MoE exchange never drops a row: where the slot-addressed
+    scratch cannot hold the worst case of a full step, the step shrinks instead; a ratio below 1
+    (the approximate mode) leaves the step alone; a decode batch that cannot fit is an error."""
+    import pytest
+    from gvirt_b200 import config
+    from gvirt_b200.models import presets
+    from gvirt_b200.parallel.moe_a2a import a2a_capacity, a2a_exact_tokens
+    from gvirt_b200.parallel.setup import fit_step_to_exchange
+    kw = dict(ep_size=8, dp_size=8, tp_size=1, max_batch_size=32, max_num_batched_tokens=8192)
+    cfg = presets.get("deepseek-v3", **kw)
+    R = 8
+    assert a2a_capacity(cfg, R, 8192) < R * 8192               # memory cuts the capacity
+    step = fit_step_to_exchange(cfg, R)
+    assert step == cfg.max_num_batched_tokens < 8192 and step % 128 == 0
+    assert R * step <= a2a_capacity(cfg, R, step)              # worst case of the new step fits
+    assert a2a_exact_tokens(cfg, R, step) == step
+    small = presets.get("qwen3-30b-a3b", **kw)
+    assert fit_step_to_exchange(small, R) == 8192              # fits as it is
+    monkeypatch.setenv("GVIRT_ACTIVE_TOKENS_RATIO_PER_EP", "0.25")
+    config.reload_flags()
+    try:
+        cfg2 = presets.get("deepseek-v3", **kw)
+        assert fit_step_to_exchange(cfg2, R) == 8192           # approximate mode: untouched
+    finally:
+        monkeypatch.delenv("GVIRT_ACTIVE_TOKENS_RATIO_PER_EP")
+        config.reload_flags()
+    # a decode batch larger than what fits exactly is refused with a clear message
+    import gvirt_b200.parallel.moe_a2a as A
+    monkeypatch.setattr(A, "a2a_capacity", lambda cfg, R, cap: 64 * R)
+    with pytest.raises(ValueError, match="decode step"):
+        fit_step_to_exchange(presets.get("deepseek-v3", **dict(kw, max_batch_size=256)), R)
