@@ -290,7 +290,9 @@ class EnvFlags:
     paranoid: bool = False               # GVIRT_PARANOID: census every op output for NaN/Inf
     paranoid_ops: bool = False           # GVIRT_PARANOID_OPS: every op call is compared with its CPU definition
     fuse_swiglu: bool = True             # GVIRT_FUSE_SWIGLU: SwiGLU in the gate/up GEMM epilogue
+    decode_l2_prefetch: bool = True      # GVIRT_DECODE_L2_PREFETCH: a decode GEMM warms L2 with the next GEMM's first tiles
     prefill_attn_tc: bool = True         # GVIRT_PREFILL_ATTN_TC: tcgen05 flash attention for 128-wide heads
+    dsa_indexer_tc: bool = True          # GVIRT_DSA_INDEXER_TC: tcgen05 lightning-indexer scores (head_dim 128)
     mla_attn_tc: bool = True             # GVIRT_MLA_ATTN_TC: tcgen05 absorbed MLA decode (128 local heads)
     fused_decode: bool = True            # GVIRT_FUSED_DECODE: dense layers at <= 128 tokens run norm, RoPE + cache
                                          # write and residual add inside the GEMM epilogues (norm weights folded)
@@ -329,7 +331,9 @@ class EnvFlags:
         f.fuse_swiglu = parse_bool(e.get("GVIRT_FUSE_SWIGLU"), f.fuse_swiglu)
         f.fused_decode = parse_bool(e.get("GVIRT_FUSED_DECODE"), f.fused_decode)
         f.prefill_attn_tc = parse_bool(e.get("GVIRT_PREFILL_ATTN_TC"), f.prefill_attn_tc)
+        f.decode_l2_prefetch = parse_bool(e.get("GVIRT_DECODE_L2_PREFETCH"), f.decode_l2_prefetch)
         f.mla_attn_tc = parse_bool(e.get("GVIRT_MLA_ATTN_TC"), f.mla_attn_tc)
+        f.dsa_indexer_tc = parse_bool(e.get("GVIRT_DSA_INDEXER_TC"), f.dsa_indexer_tc)
         f.pad_swiglu = parse_bool(e.get("GVIRT_PAD_SWIGLU"), f.pad_swiglu)
         f.a2a_scratch_gb = float(e.get("GVIRT_A2A_SCRATCH_GB", f.a2a_scratch_gb))
         f.async_scheduling = parse_bool(e.get("GVIRT_ASYNC_SCHEDULING"), f.async_scheduling)

@@ -43,6 +43,15 @@ struct Cfg {
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 };
 
+// Weight tiles of the kernel that follows in the stream: once this CTA's producer has issued its
+// last load (the epilogue phase starts, HBM would go idle), it prefetches the first `stages`
+// k-blocks of some of the follower's (tile, k-split) work items into L2. `tm` = tensor map of the
+// follower's weight with the same [128 rows x 64 columns] box.
+struct NextWeights {
+  const CUtensorMap* tm;   // null: nothing to prefetch
+  int tiles, splitk, kb_per, kb_total, stages;
+};
+
 struct Shared {
   uint8_t* ring;        // 1024-aligned stage ring
   uint64_t* full;       // [STAGES]
@@ -78,7 +87,8 @@ template <class C>
 __device__ __forceinline__ uint32_t run_mainloop(const Shared& sh, const CUtensorMap* tmP,
                                                  const CUtensorMap* tmQ, int p0, int q0, int kb0,
                                                  int nkb, unsigned int* status, int pz = -1,
-                                                 int qz = -1, int pdl_dep = 0) {
+                                                 int qz = -1, int pdl_dep = 0,
+                                                 const NextWeights* next = nullptr) {
   constexpr int BN = C::BN;
   const int warp = threadIdx.x >> 5;
   if (pdl_dep) pdl_trigger();
@@ -146,6 +156,18 @@ __device__ __forceinline__ uint32_t run_mainloop(const Shared& sh, const CUtenso
         else sm100::tma_load_2d(sp, tmP, &sh.full[s], kx, p0);
         if (qz >= 0) sm100::tma_load_3d(sq, tmQ, &sh.full[s], kx, q0, qz);
         else sm100::tma_load_2d(sq, tmQ, &sh.full[s], kx, q0);
+      }
+      if (next != nullptr && next->tm != nullptr) {
+        const int total = next->tiles * next->splitk;
+        const int me = (int)(blockIdx.x + gridDim.x * blockIdx.z), step = (int)(gridDim.x * gridDim.z);
+        for (int j = me; j < total; j += step) {
+          const int tile = j % next->tiles, z = j / next->tiles;
+          for (int s = 0; s < next->stages; ++s) {
+            const int kb = z * next->kb_per + s;
+            if (kb >= next->kb_total) break;
+            sm100::tma_prefetch_l2_2d(next->tm, kb * BK, tile * BM);
+          }
+        }
       }
     } else if (pdl_dep) {
       pdl_wait();

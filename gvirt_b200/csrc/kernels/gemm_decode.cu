@@ -71,8 +71,8 @@ __device__ __forceinline__ float rbf(float v) { return bf2f(f2bf(v)); }
 template <int BN, int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 2)
 gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
-                   bf16* out, int N, int M, int K, long long ldo, int splitk, DecEpi e,
-                   unsigned int* status) {
+                   const __grid_constant__ CUtensorMap tmNext, bf16* out, int N, int M, int K,
+                   long long ldo, int splitk, DecEpi e, NextWeights next, unsigned int* status) {
   using C = Cfg<BN, 108>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ float s_scale[BN];
@@ -86,7 +86,8 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   const int kb0 = z * kb_per;
   const int nkb = max(0, min(kb_total, kb0 + kb_per) - kb0);
 
-  const uint32_t tmem_base = run_mainloop<C>(sh, &tmW, &tmX, p0, 0, kb0, nkb, status, -1, -1, 1);
+  if (next.stages > 0) next.tm = &tmNext;
+  const uint32_t tmem_base = run_mainloop<C>(sh, &tmW, &tmX, p0, 0, kb0, nkb, status, -1, -1, 1, &next);
 
   const int quad = warp & 3;
   const int lrow = quad * 32 + lane;
@@ -275,8 +276,9 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
 }
 
 template <int BN, int MODE>
-static int launch_dec(const CUtensorMap& tmW, const CUtensorMap& tmX, bf16* out, int N, int M, int K,
-                      long long ldo, int splitk, const DecEpi& e, cudaStream_t st) {
+static int launch_dec(const CUtensorMap& tmW, const CUtensorMap& tmX, const CUtensorMap& tmNext,
+                      const NextWeights& next, bf16* out, int N, int M, int K, long long ldo, int splitk,
+                      const DecEpi& e, cudaStream_t st) {
   using C = Cfg<BN, 108>;
   auto kern = gemm_decode_kernel<BN, MODE>;
   static bool configured = false;
@@ -310,13 +312,22 @@ static int launch_dec(const CUtensorMap& tmW, const CUtensorMap& tmX, bf16* out,
   }
   cfg.attrs = attr;
   cfg.numAttrs = na;
-  cudaError_t err = cudaLaunchKernelEx(&cfg, kern, tmW, tmX, out, N, M, K, ldo, splitk, e, status_word());
+  cudaError_t err = cudaLaunchKernelEx(&cfg, kern, tmW, tmX, tmNext, out, N, M, K, ldo, splitk, e, next, status_word());
   if (err != cudaSuccess) {
     set_last_error("gemm_decode: launch", err);
     return GV_ECUDA;
   }
   return GV_OK;
 }
+
+// The weight of the GEMM that follows in the stream (set by gv_gemm_decode_next for the next
+// launch of the calling host thread, consumed by it): its first tiles are prefetched into L2 by
+// that launch's producers once their own streaming is done.
+struct NextHint {
+  const void* w;
+  long long N, K, ldw;
+};
+static thread_local NextHint t_next = {nullptr, 0, 0, 0};
 
 static int run_decode_gemm(const void* x, const void* w, void* out, long long M, long long N, long long K,
                            long long ldx, long long ldw, long long ldo, long long force_splitk,
@@ -334,12 +345,26 @@ static int run_decode_gemm(const void* x, const void* w, void* out, long long M,
   if ((rc = cached_tmap_bf16(&tmX, x, M, K, ldx, bn)) != GV_OK) return rc;
   const int sk = decode_splitk(N, K, bn, force_splitk);
   cudaStream_t st = (cudaStream_t)stream;
+  CUtensorMap tmNext = tmW;
+  NextWeights next = {nullptr, 0, 0, 0, 0, 0};
+  const NextHint hint = t_next;
+  t_next.w = nullptr;
+  if (hint.w != nullptr && cached_tmap_bf16(&tmNext, hint.w, hint.N, hint.K, hint.ldw, BM) == GV_OK) {
+    next.tiles = ceil_div(hint.N, BM);
+    next.splitk = decode_splitk(hint.N, hint.K, bn, 0);
+    next.kb_total = ceil_div(hint.K, BK);
+    next.kb_per = (next.kb_total + next.splitk - 1) / next.splitk;
+    // about what HBM delivers during an epilogue (2.5 us x 6.5 TB/s = 16 MB), 16 KB per box
+    const long long items = (long long)next.tiles * next.splitk;
+    long long stages = (16ll << 20) / (items * BM * BK * 2);
+    next.stages = (int)(stages < 1 ? 1 : stages > 8 ? 8 : stages);
+  }
 #define GV_DEC_LAUNCH(BN_)                                                                              \
   switch (e.mode) {                                                                                    \
-    case EPI_PLAIN: return launch_dec<BN_, EPI_PLAIN>(tmW, tmX, (bf16*)out, (int)N, (int)M, (int)K, ldo, sk, e, st);   \
-    case EPI_SWIGLU: return launch_dec<BN_, EPI_SWIGLU>(tmW, tmX, (bf16*)out, (int)N, (int)M, (int)K, ldo, sk, e, st); \
-    case EPI_RESID: return launch_dec<BN_, EPI_RESID>(tmW, tmX, (bf16*)out, (int)N, (int)M, (int)K, ldo, sk, e, st);   \
-    default: return launch_dec<BN_, EPI_ROPE>(tmW, tmX, (bf16*)out, (int)N, (int)M, (int)K, ldo, sk, e, st);           \
+    case EPI_PLAIN: return launch_dec<BN_, EPI_PLAIN>(tmW, tmX, tmNext, next, (bf16*)out, (int)N, (int)M, (int)K, ldo, sk, e, st);   \
+    case EPI_SWIGLU: return launch_dec<BN_, EPI_SWIGLU>(tmW, tmX, tmNext, next, (bf16*)out, (int)N, (int)M, (int)K, ldo, sk, e, st); \
+    case EPI_RESID: return launch_dec<BN_, EPI_RESID>(tmW, tmX, tmNext, next, (bf16*)out, (int)N, (int)M, (int)K, ldo, sk, e, st);   \
+    default: return launch_dec<BN_, EPI_ROPE>(tmW, tmX, tmNext, next, (bf16*)out, (int)N, (int)M, (int)K, ldo, sk, e, st);           \
   }
   switch (bn) {
     case 16: GV_DEC_LAUNCH(16)
@@ -363,6 +388,17 @@ static void set_scale(DecEpi& e, const void* ss_in, long long ss_tiles, long lon
   e.ss_ld = (int)ss_ld;
   e.inv_h = h > 0 ? 1.f / (float)h : 0.f;
   e.eps = eps;
+}
+
+// Names the weight [N, K] (row pitch ldw elements) of the GEMM that will follow the next
+// gv_gemm_decode* launch of this host thread; that launch prefetches its first tiles into L2.
+extern "C" int gv_gemm_decode_next(const void* w, long long N, long long K, long long ldw) {
+  if (w && ((K & 7) || (ldw & 7) || (reinterpret_cast<uintptr_t>(w) & 15))) return GV_EINVAL;
+  t_next.w = w;
+  t_next.N = N;
+  t_next.K = K;
+  t_next.ldw = ldw;
+  return GV_OK;
 }
 
 // out[M, N] = s_t * (x . w^T) (+ bias), or with `swiglu` out[M, N / 2] = silu(gate) * up over

@@ -99,6 +99,8 @@ int gv_gemm_decode(const void* x, const void* w, const void* bias, void* out, lo
                    long long K, long long ldx, long long ldw, long long ldo, const void* ss_in,
                    long long ss_tiles, long long ss_ld, long long norm_h, float eps, long long swiglu,
                    long long force_splitk, void* stream);
+// Weight of the GEMM that follows the next gv_gemm_decode* launch of this host thread (null clears).
+int gv_gemm_decode_next(const void* w, long long N, long long K, long long ldw);
 int gv_gemm_decode_residual(const void* x, const void* w, const void* bias, const void* residual,
                             void* x_out, void* ss_out, long long M, long long N, long long K,
                             long long ldx, long long ldw, long long ldo, long long ss_ld,
@@ -251,6 +253,12 @@ int gv_indexer_scores(const void* q, const void* w, const void* k_cache, const v
                       long long batch, long long Hi, long long D, long long block_size,
                       long long max_blocks, long long lds, long long relu, long long num_blocks,
                       void* stream);
+// tcgen05 form for D == 128, Hi % 16 == 0, Hi <= 128 (dsa_tc.cu); same arguments.
+int gv_indexer_scores_tc(const void* q, const void* w, const void* k_cache, const void* block_tables,
+                         const void* q_start, const void* cached_lens, void* scores, long long T,
+                         long long batch, long long Hi, long long D, long long block_size,
+                         long long max_blocks, long long lds, long long relu, long long num_blocks,
+                         void* stream);
 int gv_scatter_rows(const void* src, const void* slots, void* cache, long long T, long long row_bytes,
                     long long num_slots, void* stream);
 int gv_topk_select(const void* scores, long long lds, const void* lens, long long rows, long long K,

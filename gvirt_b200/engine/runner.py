@@ -212,8 +212,16 @@ class ModelRunner:
         if not self.cuda:
             return 1
         if self.cfg.attn_type in (AttnType.MLA, AttnType.DSA):
-            # the absorbed-attention kernel runs one CTA per (token, group of 32 heads, split)
-            groups = max(1, (self.cfg.num_heads // self.cfg.tp_size + 31) // 32)
+            hl = self.cfg.num_heads // self.cfg.tp_size
+            if (self.cfg.attn_type == AttnType.MLA and hl % 128 == 0 and self.cfg.kv_lora_rank == 512
+                    and self.cfg.qk_rope_head_dim == 64 and self.cfg.block_size % 32 == 0
+                    and flags().mla_attn_tc):
+                # tcgen05 kernel: one CTA per (request, 128 heads, output half, split), one CTA per
+                # SM: as many splits as fill one wave, each at least 512 keys long
+                tasks = max(1, batch * 2 * (hl // 128))
+                return max(1, min(8, self.num_sms // tasks, max(max_len, 1) // 512))
+            # the mma.sync kernel runs one CTA per (token, group of 32 heads, split)
+            groups = max(1, (hl + 31) // 32)
             c = self.rt.pick_decode_splits(batch, groups, max(max_len, 1), self.num_sms, 1, 8)
             return max(1, c.splits)
         c = self.rt.pick_decode_splits(batch, self.model.nkv, max(max_len, 1), self.num_sms, 1,

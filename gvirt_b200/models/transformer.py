@@ -205,14 +205,14 @@ class Transformer:
         return out
 
     # ------------------------------------------------------------------ fused decode forward
-    def _residual_linear(self, a, w, x, ss, ws) -> int:
+    def _residual_linear(self, a, w, x, ss, ws, next_w=None) -> int:
         """x += all_reduce_tp(a @ w^T) in place with the sums of squares of the new rows in `ss`.
         Returns how many tiles of `ss` are valid (all of them from a fused producer, one from the
         stand-alone add)."""
         ctx = self.ctx
         tiles = w.shape[0] // 128
         if ctx.tp == 1:
-            D.linear_residual(a, w, x, ss)
+            D.linear_residual(a, w, x, ss, next_w=next_w)
             return tiles
         if a.device.type == "meta":
             tmp = ws.get(tuple(x.shape), self.dtype)       # the unfused fall-back sizes the arena
@@ -261,11 +261,12 @@ class Transformer:
             o = ws.get((T, nq * hd), self.dtype)
             F.paged_attention(q, cache[0], cache[1], meta, nq, nkv, hd, 1.0, out=o)
             ws.put(q)
-            nt = self._residual_linear(o, lw.w_o, x, ss, ws)
+            nt = self._residual_linear(o, lw.w_o, x, ss, ws, next_w=lw.w_gate_up)
             ws.put(o)
             a = ws.get((T, lw.w_gate_up.shape[0] // 2), self.dtype)
-            D.linear_scaled(x, lw.w_gate_up, ss, H, eps, swiglu=True, tiles=nt, out=a)
-            nt = self._residual_linear(a, lw.w_down, x, ss, ws)
+            D.linear_scaled(x, lw.w_gate_up, ss, H, eps, swiglu=True, tiles=nt, out=a, next_w=lw.w_down)
+            nxt = self.w.layers[li + 1].w_qkv if li + 1 < len(self.w.layers) else None
+            nt = self._residual_linear(a, lw.w_down, x, ss, ws, next_w=nxt)
             ws.put(a)
         ws.put(ss)
         h = ws.get((T, H), self.dtype)

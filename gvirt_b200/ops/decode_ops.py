@@ -104,6 +104,17 @@ def add_residual_sumsq(a: torch.Tensor, x: torch.Tensor, ss: torch.Tensor) -> to
     return x
 
 
+def _hint_next(next_w: Optional[torch.Tensor]) -> None:
+    """Tell the next fused decode GEMM launch which weight the GEMM behind it will stream, so that
+    its producers warm L2 with that weight's first tiles while their own epilogue runs."""
+    if next_w is None or not next_w.is_cuda or next_w.dtype != torch.bfloat16 or not F._flags().decode_l2_prefetch:
+        return
+    import ctypes
+    fn = _native.kernels().gv_gemm_decode_next
+    fn(ctypes.c_void_p(next_w.data_ptr()), ctypes.c_longlong(next_w.shape[0]), ctypes.c_longlong(next_w.shape[1]),
+       ctypes.c_longlong(next_w.stride(0)))
+
+
 def _tiles(ss: Optional[torch.Tensor], tiles: Optional[int]):
     """(number of partial sums per token, their pitch) as the kernels take them."""
     if ss is None:
@@ -116,7 +127,8 @@ def _tiles(ss: Optional[torch.Tensor], tiles: Optional[int]):
 @F._dry
 def linear_scaled(x: torch.Tensor, w: torch.Tensor, ss: Optional[torch.Tensor], norm_h: int, eps: float,
                   bias: Optional[torch.Tensor] = None, swiglu: bool = False, tiles: Optional[int] = None,
-                  out: Optional[torch.Tensor] = None, splitk: int = 0) -> torch.Tensor:
+                  out: Optional[torch.Tensor] = None, splitk: int = 0,
+                  next_w: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out = s_t * (x @ w^T) (+ bias), s_t from `ss`; with `swiglu`, w holds [64 gate | 64 up] row
     blocks (``F.interleave_gate_up``) and out [T, N / 2] = silu(gate) * up."""
     M, K = x.shape
@@ -137,13 +149,15 @@ def linear_scaled(x: torch.Tensor, w: torch.Tensor, ss: Optional[torch.Tensor], 
         return out
     F._check_bf16(x, w, bias)
     assert M <= MAX_TOKENS and x.stride(1) == 1 and w.stride(1) == 1
+    _hint_next(next_w)
     _native.call("gemm_decode", x, w, bias, out, M, N, K, x.stride(0), w.stride(0), out.stride(0), ss, nt, ld,
                  norm_h, float(eps), int(swiglu), splitk)
     return out
 
 
 def linear_residual(a: torch.Tensor, w: torch.Tensor, x: torch.Tensor, ss_out: Optional[torch.Tensor],
-                    bias: Optional[torch.Tensor] = None, splitk: int = 0) -> torch.Tensor:
+                    bias: Optional[torch.Tensor] = None, splitk: int = 0,
+                    next_w: Optional[torch.Tensor] = None) -> torch.Tensor:
     """x += a @ w^T (+ bias) in place; ss_out[t, i] = sum of squares of the new x[t, 128 i : 128 i + 128]."""
     M, K = a.shape
     N = w.shape[0]
@@ -159,6 +173,7 @@ def linear_residual(a: torch.Tensor, w: torch.Tensor, x: torch.Tensor, ss_out: O
         return x
     F._check_bf16(a, w, x, bias)
     assert M <= MAX_TOKENS and a.stride(1) == 1 and x.stride(1) == 1
+    _hint_next(next_w)
     _native.call("gemm_decode_residual", a, w, bias, x, x, ss_out, M, N, K, a.stride(0), w.stride(0),
                  x.stride(0), ss_out.stride(0) if ss_out is not None else 0, splitk)
     return x

@@ -29,6 +29,15 @@ def indexer_scores(q, w, k_cache, meta, relu=True):
                 out[t, :n] = (w[t].float()[:, None] * dots).sum(0)
         return out
     out = torch.empty(T, L, dtype=torch.float32, device=q.device)
+    bs = meta.block_size
+    from ..config import flags
+    if (D == 128 and Hi % 16 == 0 and 16 <= Hi <= 128 and bs >= 8 and bs & (bs - 1) == 0 and T <= 65535
+            and q.dtype == torch.bfloat16 and flags().dsa_indexer_tc):
+        # keys on the TMEM lanes, heads on the columns: tcgen05 indexer (dsa_tc.cu)
+        _native.call("indexer_scores_tc", q.contiguous(), w.float().contiguous(), k_cache, meta.block_tables,
+                     meta.query_start_loc, meta.cached_lens, out, T, meta.batch, Hi, D, bs,
+                     meta.block_tables.shape[1], L, int(relu), k_cache.shape[0])
+        return out
     _native.call("indexer_scores", q.contiguous(), w.contiguous(), k_cache, meta.block_tables,
                  meta.query_start_loc, meta.cached_lens, out, T, meta.batch, Hi, D, meta.block_size,
                  meta.block_tables.shape[1], L, int(relu), k_cache.shape[0])

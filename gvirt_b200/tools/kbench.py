@@ -199,9 +199,9 @@ def case_layer(args):
         gate/up GEMM with SwiGLU, down_proj with the residual add; RMSNorm inside the epilogues."""
         D.linear_rope(res, wqkv[li], m, cos_sin, kcs[li], vcs[li], nq, nkv, ss, H, 1e-5, out=qd)
         F.paged_attention(qd, kcs[li], vcs[li], m, nq, nkv, 128, out=ao)
-        D.linear_residual(ao, wo[li], res, ss)
-        D.linear_scaled(res, wgu[li], ss, H, 1e-5, swiglu=True, out=act)
-        D.linear_residual(act, wd[li], res, ss)
+        D.linear_residual(ao, wo[li], res, ss, next_w=wgu[li])
+        D.linear_scaled(res, wgu[li], ss, H, 1e-5, swiglu=True, out=act, next_w=wd[li])
+        D.linear_residual(act, wd[li], res, ss, next_w=wqkv[(li + 1) % L])
 
     wbytes = (wqkv[0].numel() + wo[0].numel() + wgu[0].numel() + wd[0].numel()) * 2
     kvbytes = B * ctx * nkv * 128 * 2 * 2

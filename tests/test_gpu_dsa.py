@@ -106,3 +106,31 @@ def test_masked_attention_matches_reference_and_gathered(mode):
         mla_ops.mla_attention(qf.to(DEV), dense.view(B, K, 1, dc + dr), md, heads, dc, dr, scale, out=got2)
         close(got2, want, atol=1e-2, rtol=3e-2, what="gathered dense attention")
     status_ok()
+
+
+@pytest.mark.parametrize("Hi,bs", [(64, 64), (32, 128), (128, 16)])
+def test_indexer_scores_tensor_core_path_long_context(Hi, bs):
+    """tcgen05 indexer (keys on the TMEM lanes) over a long and two short contexts, several key
+    tiles per CTA, against the CUDA-core kernel and the fp32 definition."""
+    from gvirt_b200 import _native
+    D = 128
+    lens, cached = [1, 3, 1], [9000, 130, 0]
+    _, _, _, mc, _ = build(lens, cached, 1, 1, 64, bs)
+    m = _to_dev(mc)
+    T = sum(lens)
+    g = torch.Generator().manual_seed(Hi)
+    nblk = int(mc.block_tables.max()) + 1
+    kc = (torch.randn(nblk, bs, 1, D, generator=g) * 0.3).bfloat16()
+    q = (torch.randn(T, Hi, D, generator=g) * 0.3).bfloat16()
+    w = torch.randn(T, Hi, generator=g)
+    want = dsa_ops.indexer_scores(q, w, kc, mc, True)
+    got = dsa_ops.indexer_scores(q.to(DEV), w.to(DEV), kc.to(DEV), m, True)
+    L = want.shape[1]
+    old = torch.empty(T, L, dtype=torch.float32, device=DEV)
+    _native.call("indexer_scores", q.to(DEV), w.to(DEV), kc.to(DEV), m.block_tables, m.query_start_loc,
+                 m.cached_lens, old, T, m.batch, Hi, D, bs, m.block_tables.shape[1], L, 1, nblk)
+    fin = torch.isfinite(want)
+    assert torch.equal(torch.isfinite(got.cpu()), fin) and torch.equal(torch.isfinite(old.cpu()), fin)
+    close(got.cpu()[fin], want[fin], atol=5e-2, rtol=2e-2, what="tcgen05 indexer vs definition")
+    close(got.cpu()[fin], old.cpu()[fin], atol=5e-2, rtol=2e-2, what="tcgen05 indexer vs CUDA-core kernel")
+    status_ok()
