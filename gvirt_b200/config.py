@@ -290,7 +290,8 @@ class EnvFlags:
     paranoid: bool = False               # GVIRT_PARANOID: census every op output for NaN/Inf
     paranoid_ops: bool = False           # GVIRT_PARANOID_OPS: every op call is compared with its CPU definition
     fuse_swiglu: bool = True             # GVIRT_FUSE_SWIGLU: SwiGLU in the gate/up GEMM epilogue
-    decode_l2_prefetch: bool = True      # GVIRT_DECODE_L2_PREFETCH: a decode GEMM warms L2 with the next GEMM's first tiles
+    decode_l2_prefetch: bool = False     # GVIRT_DECODE_L2_PREFETCH: a decode GEMM warms L2 with the next GEMM's first
+                                         # tiles (measured: +3.6 us per Llama-3-8B layer at TP1, so off)
     prefill_attn_tc: bool = True         # GVIRT_PREFILL_ATTN_TC: tcgen05 flash attention for 128-wide heads
     dsa_indexer_tc: bool = True          # GVIRT_DSA_INDEXER_TC: tcgen05 lightning-indexer scores (head_dim 128)
     mla_attn_tc: bool = True             # GVIRT_MLA_ATTN_TC: tcgen05 absorbed MLA decode (128 local heads)
@@ -301,9 +302,10 @@ class EnvFlags:
     async_scheduling: bool = True        # GVIRT_ASYNC_SCHEDULING: prepare step k + 1 on the host during step k
     symm_max_bytes: int = 8 << 20        # GVIRT_SYMM_MAX_BYTES: largest payload of the own collectives
     sp_max_ranks: int = 2                # GVIRT_SP_MAX_RANKS: sequence-parallel layer loop up to this TP size
-    prefill_gemm_persistent: int = 0     # GVIRT_PREFILL_GEMM_PERSISTENT: GEMMs with >= 1024 rows through a persistent
-                                         # kernel with a double-buffered accumulator: 1 = the grouped kernel with one
-                                         # segment (128 x 128 tiles, bias-free only), 2 = token-major 128 x 256 tiles
+    prefill_gemm_persistent: int = 3     # GVIRT_PREFILL_GEMM_PERSISTENT: GEMMs with >= 1024 rows through a persistent
+                                         # kernel with a double-buffered accumulator: 0 = never, 1 = the grouped kernel
+                                         # with one segment (128 x 128 tiles, bias-free only), 2 = token-major 128 x 256
+                                         # tiles always, 3 = token-major 128 x 256 tiles for outputs up to 8192 wide
     nvtx: bool = False                   # GVIRT_NVTX: an NVTX range around every kernel launcher call and engine step
     cpu_binding: bool = False            # GVIRT_CPU_BINDING: pin each rank to the host cores next to its GPU
     mixed_batches: bool = False          # GVIRT_MIXED_BATCHES: decoding requests ride along with prefill chunks
@@ -340,7 +342,8 @@ class EnvFlags:
         f.symm_max_bytes = int(e.get("GVIRT_SYMM_MAX_BYTES", f.symm_max_bytes))
         f.sp_max_ranks = int(e.get("GVIRT_SP_MAX_RANKS", f.sp_max_ranks))
         v = (e.get("GVIRT_PREFILL_GEMM_PERSISTENT") or "").strip().lower()
-        f.prefill_gemm_persistent = int(v) if v.isdigit() else int(parse_bool(v or None, False))
+        if v:
+            f.prefill_gemm_persistent = int(v) if v.isdigit() else int(parse_bool(v, False))
         f.nvtx = parse_bool(e.get("GVIRT_NVTX"), f.nvtx)
         f.cpu_binding = parse_bool(e.get("GVIRT_CPU_BINDING"), f.cpu_binding)
         f.mixed_batches = parse_bool(e.get("GVIRT_MIXED_BATCHES"), f.mixed_batches)

@@ -41,6 +41,8 @@ namespace gemm {
 int cached_tmap_bf16(CUtensorMap* out, const void* base, long long rows, long long cols,
                      long long row_stride_elems, int box_rows);
 
+void take_next_weights(int bn, CUtensorMap* tm, NextWeights* nx);   // gemm_decode.cu
+
 constexpr int AR_MAX_RANKS = 8;
 
 struct ArArgs {
@@ -225,8 +227,9 @@ __device__ __forceinline__ bool copy_final_lines(const uint4* __restrict__ fin, 
 template <int BN>
 __global__ void __launch_bounds__(NUM_THREADS, 2)
 gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
-                      bf16* out, const bf16* __restrict__ bias, const bf16* residual, int N, int M,
-                      int K, long long ldo, int splitk, ArArgs a, unsigned int* status) {
+                      const __grid_constant__ CUtensorMap tmNext, bf16* out, const bf16* __restrict__ bias,
+                      const bf16* residual, int N, int M, int K, long long ldo, int splitk, ArArgs a,
+                      NextWeights next, unsigned int* status) {
   using C = Cfg<BN, 108>;
   extern __shared__ uint8_t smem_raw[];
   const Shared sh = carve<C>(smem_raw);
@@ -240,7 +243,8 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
   const int cta = blockIdx.x + gridDim.x * blockIdx.z;
 
   // weights (P) are constant and are prefetched before the wait on the kernel in front
-  const uint32_t tmem_base = run_mainloop<C>(sh, &tmW, &tmX, p0, 0, kb0, nkb, status, -1, -1, 1);
+  if (next.stages > 0) next.tm = &tmNext;
+  const uint32_t tmem_base = run_mainloop<C>(sh, &tmW, &tmX, p0, 0, kb0, nkb, status, -1, -1, 1, &next);
   // the channel generation is bumped by the previous user of the channel: read it after the wait
   const unsigned int gen = *reinterpret_cast<volatile unsigned int*>(&a.state[0]) + 1u;
 
@@ -405,7 +409,8 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
 template <int BN>
 static int launch_ar(const CUtensorMap& tmW, const CUtensorMap& tmX, bf16* out, const bf16* bias,
                      const bf16* residual, int N, int M, int K, long long ldo, int splitk,
-                     const ArArgs& a, cudaStream_t st) {
+                     const ArArgs& a, cudaStream_t st, const CUtensorMap& tmNextIn, const NextWeights& next) {
+  CUtensorMap tmNext = next.stages > 0 ? tmNextIn : tmW;
   using C = Cfg<BN, 108>;
   static_assert(C::STAGES * C::STAGE_BYTES >= BN * BM * 6, "staging must fit in the ring");
   auto kern = gemm_allreduce_kernel<BN>;
@@ -440,8 +445,8 @@ static int launch_ar(const CUtensorMap& tmW, const CUtensorMap& tmX, bf16* out, 
   }
   cfg.attrs = attr;
   cfg.numAttrs = na;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmW, tmX, out, bias, residual, N, M, K, ldo, splitk,
-                                     a, status_word());
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmW, tmX, tmNext, out, bias, residual, N, M, K, ldo, splitk,
+                                     a, next, status_word());
   if (e != cudaSuccess) {
     set_last_error("gemm_allreduce: launch", e);
     return GV_ECUDA;
@@ -466,6 +471,12 @@ extern "C" int gv_gemm_allreduce_ss(const void* x, const void* w, const void* bi
                                     long long recv_off, long long flags_off, void* state,
                                     long long rank, long long R, long long m_cap,
                                     long long max_ctas, long long two_shot, void* stream) {
+  CUtensorMap tmNext;
+  NextWeights next = {nullptr, 0, 0, 0, 0, 0};
+  {
+    const int bn0 = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
+    take_next_weights((M > 0 && M <= 128) ? bn0 : 0, &tmNext, &next);   // consumed even if the launch is refused
+  }
   if (!x || !w || !out || !peers || !state || M <= 0 || N <= 0 || K <= 0) return GV_EINVAL;
   if (ss_out && ((N % 128) || ss_ld < N / 128)) return GV_EINVAL;
   if ((K & 7) || (ldx & 7) || (ldw & 7) || (N & 7) || (ldo & 7)) return GV_EINVAL;
@@ -500,10 +511,10 @@ extern "C" int gv_gemm_allreduce_ss(const void* x, const void* w, const void* bi
   a.ss_ld = (int)ss_ld;
   cudaStream_t st = (cudaStream_t)stream;
   switch (bn) {
-    case 16: return launch_ar<16>(tmW, tmX, (bf16*)out, (const bf16*)bias, (const bf16*)residual, (int)N, (int)M, (int)K, ldo, sk, a, st);
-    case 32: return launch_ar<32>(tmW, tmX, (bf16*)out, (const bf16*)bias, (const bf16*)residual, (int)N, (int)M, (int)K, ldo, sk, a, st);
-    case 64: return launch_ar<64>(tmW, tmX, (bf16*)out, (const bf16*)bias, (const bf16*)residual, (int)N, (int)M, (int)K, ldo, sk, a, st);
-    default: return launch_ar<128>(tmW, tmX, (bf16*)out, (const bf16*)bias, (const bf16*)residual, (int)N, (int)M, (int)K, ldo, sk, a, st);
+    case 16: return launch_ar<16>(tmW, tmX, (bf16*)out, (const bf16*)bias, (const bf16*)residual, (int)N, (int)M, (int)K, ldo, sk, a, st, tmNext, next);
+    case 32: return launch_ar<32>(tmW, tmX, (bf16*)out, (const bf16*)bias, (const bf16*)residual, (int)N, (int)M, (int)K, ldo, sk, a, st, tmNext, next);
+    case 64: return launch_ar<64>(tmW, tmX, (bf16*)out, (const bf16*)bias, (const bf16*)residual, (int)N, (int)M, (int)K, ldo, sk, a, st, tmNext, next);
+    default: return launch_ar<128>(tmW, tmX, (bf16*)out, (const bf16*)bias, (const bf16*)residual, (int)N, (int)M, (int)K, ldo, sk, a, st, tmNext, next);
   }
 }
 

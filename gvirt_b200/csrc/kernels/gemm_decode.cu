@@ -75,7 +75,6 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
                    long long ldo, int splitk, DecEpi e, NextWeights next, unsigned int* status) {
   using C = Cfg<BN, 108>;
   extern __shared__ uint8_t smem_raw[];
-  __shared__ float s_scale[BN];
   const Shared sh = carve<C>(smem_raw);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile = blockIdx.x;
@@ -86,12 +85,6 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   const int kb0 = z * kb_per;
   const int nkb = max(0, min(kb_total, kb0 + kb_per) - kb0);
 
-  if (next.stages > 0) next.tm = &tmNext;
-  const uint32_t tmem_base = run_mainloop<C>(sh, &tmW, &tmX, p0, 0, kb0, nkb, status, -1, -1, 1, &next);
-
-  const int quad = warp & 3;
-  const int lrow = quad * 32 + lane;
-  float* red = reinterpret_cast<float*>(sh.ring);  // fp32 [BN][128]; the ring is idle by now
   // finishing phase geometry: epilogue warp `ew` owns the columns c = z + (ew + 4 i) * splitk
   const int ew = warp - 2;
   const int ncols = (BN - z + splitk - 1) / splitk;
@@ -99,25 +92,50 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   const int p = p0 + r4;
   const bool p_ok = p + 4 <= N;                      // N % 4 == 0 is enforced by the launcher
   const int kind = tile < e.nq ? 0 : (tile < e.nq + e.nkv ? 1 : 2);   // EPI_ROPE: q, k or v head
-  // Inputs of a column's finishing step that do not depend on the accumulator. They are fetched
-  // for the first NPRE columns of a warp while the main loop is still running: the dependent
-  // chain position -> cos / sin row (two trips to L2) is off the critical path by then.
+  // Positions and cache slots are inputs of the step (copied in before its first kernel), not
+  // products of the kernel in front: they may be read ahead of the dependency wait, which takes
+  // the first half of the position -> cos / sin chain out of the epilogue.
+  long long pos_pre[4] = {0, 0, 0, 0};
+  int slot_pre[4] = {-1, -1, -1, -1};
+  if (MODE == EPI_ROPE && warp >= 2) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int ci = ew + 4 * i;
+      const int c = z + ci * splitk;
+      if (ci < ncols && c < M) {
+        if (kind != 2) pos_pre[i] = e.positions[c];
+        if (kind != 0) slot_pre[i] = e.slots[c];
+      }
+    }
+  }
+  if (next.stages > 0) next.tm = &tmNext;
+  const uint32_t tmem_base = run_mainloop<C>(sh, &tmW, &tmX, p0, 0, kb0, nkb, status, -1, -1, 1, &next);
+
+  const int quad = warp & 3;
+  const int lrow = quad * 32 + lane;
+  float* red = reinterpret_cast<float*>(sh.ring);  // fp32 [BN][128]; the ring is idle by now
+  // Inputs of a column's finishing step that do not depend on the accumulator (RMSNorm partial
+  // sums, residual row, cos / sin row, cache slot). For the first NPRE columns of a warp they are
+  // requested while the main loop is still running, every load of every column issued before the
+  // first one is consumed, so their latencies overlap each other and the MMAs.
   struct Side {
     float r[4];          // EPI_RESID: residual row; EPI_ROPE: cos
     float sn[4];         // EPI_ROPE: sin
     int slot;            // EPI_ROPE: cache slot of k / v heads
+    float scale;         // RMSNorm factor of the token (1 without ss_in)
   };
-  auto load_side = [&](int c, Side& sd) {
-    sd.slot = -1;
+  auto load_side = [&](int c, long long pos, int slot, Side& sd) {
+    sd.slot = slot;
+    sd.scale = 0.f;
 #pragma unroll
     for (int j = 0; j < 4; ++j) sd.r[j] = sd.sn[j] = 0.f;
     if (c >= M) return;
+    if (e.ss_in != nullptr)
+      for (int t = lane; t < e.ss_tiles; t += 32) sd.scale += e.ss_in[(long long)c * e.ss_ld + t];
     if (MODE == EPI_RESID) {
       if (p_ok) unpack4f(*reinterpret_cast<const uint2*>(e.residual + (long long)c * ldo + p), sd.r);
     } else if (MODE == EPI_ROPE) {
-      if (kind != 0) sd.slot = e.slots[c];
       if (kind != 2) {
-        long long pos = e.positions[c];
         if (pos < 0 || pos >= e.max_pos) {
           if (lane == 0) atomicOr(status, GV_ST_BAD_INDEX);
           pos = 0;
@@ -130,32 +148,21 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       }
     }
   };
+  auto finish_side = [&](Side& sd) {     // every lane of the warp calls it
+    sd.scale = e.ss_in != nullptr ? rsqrtf(warp_sum(sd.scale) * e.inv_h + e.eps) : 1.f;
+  };
   constexpr int NPRE = 4;
   Side pre[NPRE];
   float b4[4] = {0.f, 0.f, 0.f, 0.f};
   if (warp >= 2) {
-    // token scales: a warp sums the partial sums of squares of one token (lanes over tiles)
-    for (int c0 = ew * 4; c0 < BN; c0 += 16) {
-      float acc[4] = {0.f, 0.f, 0.f, 0.f};
-      if (e.ss_in != nullptr) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          if (c0 + j < M)
-            for (int t = lane; t < e.ss_tiles; t += 32) acc[j] += e.ss_in[(long long)(c0 + j) * e.ss_ld + t];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) acc[j] = warp_sum(acc[j]);
-      }
-      if (lane < 4 && c0 + lane < BN) {
-        const float a = lane == 0 ? acc[0] : lane == 1 ? acc[1] : lane == 2 ? acc[2] : acc[3];
-        s_scale[c0 + lane] = e.ss_in != nullptr ? rsqrtf(a * e.inv_h + e.eps) : 1.f;
-      }
-    }
     if (e.bias != nullptr && p_ok) unpack4f(*reinterpret_cast<const uint2*>(e.bias + p), b4);
 #pragma unroll
     for (int i = 0; i < NPRE; ++i) {
       const int ci = ew + 4 * i;
-      load_side(ci < ncols ? z + ci * splitk : M, pre[i]);
+      load_side(ci < ncols ? z + ci * splitk : M, pos_pre[i], slot_pre[i], pre[i]);
     }
+#pragma unroll
+    for (int i = 0; i < NPRE; ++i) finish_side(pre[i]);
     wait_accum(sh, status);
 #pragma unroll 1
     for (int c = 0; c < BN; c += 16) {
@@ -179,7 +186,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         const float4 t = *reinterpret_cast<const float4*>(&red[c * BM + r4]);
         a[0] = t.x; a[1] = t.y; a[2] = t.z; a[3] = t.w;
       }
-      const float sc = s_scale[c];
+      const float sc = sd.scale;
       if (MODE == EPI_PLAIN) {
         if (p_ok) {
           float o[4];
@@ -266,7 +273,14 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         for (int k = 1; k < NPRE; ++k)
           if (i == k) sd = pre[k];
       } else {
-        load_side(c, sd);
+        long long pos = 0;
+        int slot = -1;
+        if (MODE == EPI_ROPE) {
+          if (kind != 2) pos = e.positions[c];
+          if (kind != 0) slot = e.slots[c];
+        }
+        load_side(c, pos, slot, sd);
+        finish_side(sd);
       }
       column(c, sd);
     }
@@ -329,36 +343,42 @@ struct NextHint {
 };
 static thread_local NextHint t_next = {nullptr, 0, 0, 0};
 
+// Consumes the hint: fills `tm` / `nx` for a launch with a `bn`-token tile (nx->stages stays 0
+// when there is no hint). Also used by the fused GEMM + all-reduce launcher.
+void take_next_weights(int bn, CUtensorMap* tm, NextWeights* nx) {
+  const NextHint hint = t_next;
+  t_next.w = nullptr;                      // a hint serves exactly one launch attempt
+  if (bn <= 0 || hint.w == nullptr || cached_tmap_bf16(tm, hint.w, hint.N, hint.K, hint.ldw, BM) != GV_OK) return;
+  nx->tiles = ceil_div(hint.N, BM);
+  nx->splitk = decode_splitk(hint.N, hint.K, bn, 0);
+  nx->kb_total = ceil_div(hint.K, BK);
+  nx->kb_per = (nx->kb_total + nx->splitk - 1) / nx->splitk;
+  // about what HBM delivers during an epilogue (2.5 us x 6.5 TB/s = 16 MB), 16 KB per box
+  const long long items = (long long)nx->tiles * nx->splitk;
+  const long long stages = (16ll << 20) / (items * BM * BK * 2);
+  nx->stages = (int)(stages < 1 ? 1 : stages > 8 ? 8 : stages);
+}
+
 static int run_decode_gemm(const void* x, const void* w, void* out, long long M, long long N, long long K,
                            long long ldx, long long ldw, long long ldo, long long force_splitk,
                            const DecEpi& e, void* stream) {
+  const int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
+  CUtensorMap tmNext;
+  NextWeights next = {nullptr, 0, 0, 0, 0, 0};
+  take_next_weights((w && M > 0 && M <= 128) ? bn : 0, &tmNext, &next);   // consumed even if the launch is refused
   if (!x || !w || !out || M <= 0 || N <= 0 || K <= 0) return GV_EINVAL;
   if ((K & 7) || (ldx & 7) || (ldw & 7) || (N & 3) || (ldo & 3)) return GV_EINVAL;
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return GV_EINVAL;
   if (reinterpret_cast<uintptr_t>(out) & 7) return GV_EINVAL;
   if (M > 128) return GV_EUNSUPPORTED;
   if (e.ss_in != nullptr && (e.ss_tiles <= 0 || e.ss_ld < e.ss_tiles)) return GV_EINVAL;
-  const int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
   CUtensorMap tmW, tmX;
   int rc;
   if ((rc = cached_tmap_bf16(&tmW, w, N, K, ldw, BM)) != GV_OK) return rc;
   if ((rc = cached_tmap_bf16(&tmX, x, M, K, ldx, bn)) != GV_OK) return rc;
   const int sk = decode_splitk(N, K, bn, force_splitk);
   cudaStream_t st = (cudaStream_t)stream;
-  CUtensorMap tmNext = tmW;
-  NextWeights next = {nullptr, 0, 0, 0, 0, 0};
-  const NextHint hint = t_next;
-  t_next.w = nullptr;
-  if (hint.w != nullptr && cached_tmap_bf16(&tmNext, hint.w, hint.N, hint.K, hint.ldw, BM) == GV_OK) {
-    next.tiles = ceil_div(hint.N, BM);
-    next.splitk = decode_splitk(hint.N, hint.K, bn, 0);
-    next.kb_total = ceil_div(hint.K, BK);
-    next.kb_per = (next.kb_total + next.splitk - 1) / next.splitk;
-    // about what HBM delivers during an epilogue (2.5 us x 6.5 TB/s = 16 MB), 16 KB per box
-    const long long items = (long long)next.tiles * next.splitk;
-    long long stages = (16ll << 20) / (items * BM * BK * 2);
-    next.stages = (int)(stages < 1 ? 1 : stages > 8 ? 8 : stages);
-  }
+  if (next.stages == 0) tmNext = tmW;      // unused, but a valid map
 #define GV_DEC_LAUNCH(BN_)                                                                              \
   switch (e.mode) {                                                                                    \
     case EPI_PLAIN: return launch_dec<BN_, EPI_PLAIN>(tmW, tmX, tmNext, next, (bf16*)out, (int)N, (int)M, (int)K, ldo, sk, e, st);   \

@@ -220,7 +220,7 @@ class Transformer:
             return tiles
         heap = ctx.symm
         if heap is not None and a.is_cuda and heap.can_fuse_gemm_ar(a, w):
-            heap.gemm_allreduce(a, w, out=x, residual=x, ss_out=ss)
+            heap.gemm_allreduce(a, w, out=x, residual=x, ss_out=ss, next_w=next_w)
             return tiles
         tmp = ws.get(tuple(x.shape), self.dtype)
         F.linear(a, w, None, out=tmp)

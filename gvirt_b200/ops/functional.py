@@ -93,6 +93,11 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
     assert o2.stride(-1) == 1
     if M > 0:
         mode = _flags().prefill_gemm_persistent if M >= 1024 else 0
+        if mode == 3:
+            # measured at 8192 tokens (Llama-3-8B shapes): the persistent kernel wins on the narrow
+            # outputs (qkv 359 vs 429 us, o_proj 230 vs 249, down 727 vs 824) and loses on the wide
+            # gate/up (1972 vs 1766), whose many tiles already hide the epilogue
+            mode = 2 if N <= 8192 else 0
         if mode == 2 and N % 8 == 0 and o2.stride(0) % 8 == 0 and o2.data_ptr() % 16 == 0:
             # token-major 128 x 256 tiles, one CTA per SM walking the tile list with the accumulator
             # double-buffered in TMEM: a tile's epilogue overlaps the next tile's main loop

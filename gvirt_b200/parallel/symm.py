@@ -260,7 +260,8 @@ class SymmetricHeap:
     # ------------------------------------------------------------------ fused GEMM + all-reduce
     def gemm_allreduce(self, x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
                        bias: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
-                       tag: Optional[str] = None, ss_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                       tag: Optional[str] = None, ss_out: Optional[torch.Tensor] = None,
+                       next_w: Optional[torch.Tensor] = None) -> torch.Tensor:
         """out = sum_r x_r @ w_r^T (+ bias) (+ residual); see csrc/kernels/gemm_allreduce.cu.
         `out` may be `residual` itself (the residual stream updated in place); `ss_out` fp32
         [tokens, N / 128] receives the sums of squares of the new rows per 128-feature tile."""
@@ -274,6 +275,9 @@ class SymmetricHeap:
         name = tag or f"gemm_ar:{N}x{K}"
         # receive region per parity: [R sources + 1 final][m_cap tokens][N / 4] sixteen-byte lines
         ch = self.channel(name, (self.world + 1) * m_cap * N * 4, 2 * self.num_sms)
+        if next_w is not None:
+            from ..ops.decode_ops import _hint_next
+            _hint_next(next_w)          # this launch warms L2 with the first tiles of the GEMM behind it
         _native.call("gemm_allreduce_ss", x2, w, bias, residual, o2, ss_out,
                      ss_out.stride(0) if ss_out is not None else 0, M, N, K, x2.stride(0), w.stride(0),
                      o2.stride(0), self.peers, ch.data_off, ch.flags_off, ch.state, self.rank, self.world,

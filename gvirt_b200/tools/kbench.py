@@ -296,6 +296,45 @@ def case_rope(args):
     _report("rope", us, nbytes, args, tokens=T, generic_kernel=bool(os.environ.get("GVIRT_DISABLE_ROPE_FAST")))
 
 
+def case_decode_gemm(args):
+    """The fused decode GEMMs of one Llama-3-8B layer at `--tp` shapes, each timed on its own over
+    rotating weights: QKV + RoPE + cache write, o_proj + residual, gate/up + SwiGLU, down + residual."""
+    from ..ops import decode_ops as D
+    dev = "cuda"
+    TP, B, H = args.tp, args.batch, 4096
+    nq, nkv, inter = 32 // TP, max(1, 8 // TP), 14336 // TP
+    m, nblk = _meta(B, args.ctx, 128, dev)
+    copies = 2 if args.eager else 6          # a profiler capture wants a small footprint
+    kc = (torch.randn(nblk, 128, nkv, 128, device=dev) * 0.5).bfloat16()
+    vc = torch.zeros_like(kc)
+
+    def mk(n, k):
+        return [(torch.randn(n, k, device=dev) * 0.02).bfloat16() for _ in range(copies)]
+
+    wqkv, wo, wgu, wd = mk((nq + 2 * nkv) * 128, H), mk(H, nq * 128), mk(2 * inter, H), mk(H, inter)
+    x = torch.randn(B, H, device=dev).bfloat16()
+    ss = D.new_sumsq(H, dev)
+    qd = torch.empty(B, nq * 128, device=dev, dtype=torch.bfloat16)
+    ao = torch.randn(B, nq * 128, device=dev).bfloat16()
+    act = torch.randn(B, inter, device=dev).bfloat16()
+    act_o = torch.empty_like(act)
+    cos_sin = torch.randn(8192, 128, device=dev)
+    D.linear_residual(ao, wo[0], x, ss)
+    out = {"case": "decode_gemm", "tp": TP, "batch": B}
+    peak = _peak(args)
+    for name, fn, nbytes in (
+            ("qkv_rope", lambda i: D.linear_rope(x, wqkv[i % copies], m, cos_sin, kc, vc, nq, nkv, ss, H, 1e-5, out=qd),
+             wqkv[0].numel() * 2),
+            ("o_proj_residual", lambda i: D.linear_residual(ao, wo[i % copies], x, ss), wo[0].numel() * 2),
+            ("gate_up_swiglu", lambda i: D.linear_scaled(x, wgu[i % copies], ss, H, 1e-5, swiglu=True, out=act_o),
+             wgu[0].numel() * 2),
+            ("down_residual", lambda i: D.linear_residual(act, wd[i % copies], x, ss), wd[0].numel() * 2)):
+        us = _time_us(fn, args)
+        out[name] = {"us": round(us, 2), "GB_s": round(nbytes / us / 1e3, 1),
+                     "hbm_fraction_of_measured": round(nbytes / us / 1e3 / peak, 3)}
+    print(json.dumps(out), flush=True)
+
+
 def case_prefill_attn(args):
     """Causal prefill attention over `--batch` requests of `--tokens` new tokens each (no cached
     prefix), 128-wide heads: the tcgen05 kernel against the mma.sync kernel, TFLOP/s counted as
@@ -323,7 +362,7 @@ def case_prefill_attn(args):
 
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("case", choices=["gemm", "swiglu", "attn", "mla", "layer", "prefill_gemm", "rope", "prefill_attn"])
+    ap.add_argument("case", choices=["gemm", "swiglu", "attn", "mla", "layer", "prefill_gemm", "rope", "prefill_attn", "decode_gemm"])
     ap.add_argument("--tokens", type=int, default=8192)
     ap.add_argument("--with-persistent", action="store_true",
                     help="prefill_gemm: also time gemm_persist.cu (GVIRT_PREFILL_GEMM_PERSISTENT=2)")
@@ -348,7 +387,7 @@ def main() -> int:
     torch.manual_seed(0)
     {"gemm": case_gemm, "swiglu": lambda a: case_gemm(a, True), "attn": case_attn, "mla": case_mla,
      "layer": case_layer, "prefill_gemm": case_prefill_gemm, "rope": case_rope,
-     "prefill_attn": case_prefill_attn}[args.case](args)
+     "prefill_attn": case_prefill_attn, "decode_gemm": case_decode_gemm}[args.case](args)
     st = _native.read_status()
     if st:
         print(json.dumps({"status_word": st, "meaning": _native.describe_status(st)}))
