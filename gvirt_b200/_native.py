@@ -44,6 +44,10 @@ def kernels() -> ctypes.CDLL:
                 lib.gv_status_ptr.restype = ctypes.c_void_p
                 lib.gv_gemm_set_splitk.argtypes = [ctypes.c_longlong] * 4
                 lib.gv_set_pdl.argtypes = [ctypes.c_longlong]
+                lib.gv_set_prefill_tc_warpgroups.argtypes = [ctypes.c_longlong]
+                lib.gv_set_prefill_tc_warpgroups.restype = None
+                lib.gv_set_decode_variant.argtypes = [ctypes.c_longlong]
+                lib.gv_set_decode_variant.restype = None
                 lib.gv_set_sm_budget.argtypes = [ctypes.c_longlong]
                 lib.gv_set_sm_budget.restype = ctypes.c_longlong
                 lib.gv_planned_sms.restype = ctypes.c_longlong

@@ -40,7 +40,6 @@ constexpr int BN = 128;             // keys per tile
 constexpr int TILE_BYTES = 128 * 128 * 2;   // one 128 x 128 bf16 tile = two 64-column chunks
 constexpr int CHUNK_BYTES = 128 * 128;      // 128 rows x 128 bytes
 constexpr int KV_STAGES = 2;
-constexpr int THREADS = 192;
 constexpr int TMEM_COLS = 512;      // S0 [0,128) S1 [128,256) O [256,384)
 constexpr float RESCALE_LOG2 = 8.f; // move the running maximum only past this gap (log2 units)
 
@@ -53,9 +52,10 @@ struct Bars {
   uint32_t tmem_slot;
 };
 
-constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 * KV_STAGES + 1) + 1024 + sizeof(Bars);
+constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 * KV_STAGES + 1) + 1024 + sizeof(Bars) + 3 * 256 * 4;
 
-__global__ void __launch_bounds__(THREADS, 1)
+template <int WG>
+__global__ void __launch_bounds__(64 + 128 * WG, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const int* __restrict__ block_tables,
                   const int* __restrict__ q_start, const int* __restrict__ cached_lens,
@@ -95,9 +95,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     }
     for (int s = 0; s < 2; ++s) {
       sm100::mbar_init(&bars->s_full[s], 1);
-      sm100::mbar_init(&bars->s_empty[s], 128);
+      sm100::mbar_init(&bars->s_empty[s], 128 * WG);
     }
-    sm100::mbar_init(&bars->p_full, 128);
+    sm100::mbar_init(&bars->p_full, 128 * WG);
     sm100::mbar_init(&bars->pv_done, 1);
     sm100::mbar_fence_init();
   }
@@ -209,42 +209,56 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     }
   } else {
     // ------------------------------------------------------------------ softmax + epilogue
+    // WG warp groups of 4 warps: with WG == 2 the warps w and w + 4 share the 32 query rows of
+    // their TMEM quadrant and each takes one 64-key half of every score row, which doubles the
+    // warps per scheduler (exponentials and conversions of one hide the latencies of the other).
+    constexpr int COLS = BN / WG;                      // score columns per thread
     const int quad = warp & 3;
+    const int half = WG == 2 ? (warp - 2) >> 2 : 0;    // which half of the columns
     const int r = quad * 32 + lane;                    // query row = TMEM lane
     const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
     const int qi = q_lo + r;                           // token index inside the request
     const int limit = min(cached + qi, kv_end - 1);    // last visible key of this row
+    float* xch = reinterpret_cast<float*>(bars + 1);   // [2][128] row maxima / sums of the two halves
+    auto pair_bar = [&]() {                            // the two warps that share this row range
+      if (WG == 2) asm volatile("bar.sync %0, 64;" ::"r"(2 + quad) : "memory");
+    };
     float m = -INFINITY, l = 0.f;
     bool ok = true;
-    for (int t = 0; t < ntiles && ok; ++t) {
+    // A wait that runs out only clears `ok`: the thread keeps walking the loop (without further
+    // waits), so that every named barrier and every warp-collective TMEM access below still sees
+    // all of its participants and the kernel ends.
+    for (int t = 0; t < ntiles; ++t) {
       const int sb = t & 1;
       const uint32_t sph = (uint32_t)(t >> 1) & 1u;
-      if (!sm100::mbar_wait(&bars->s_full[sb], sph)) {
-        ok = false;
-        break;
-      }
+      if (ok && !sm100::mbar_wait(&bars->s_full[sb], sph)) ok = false;
       sm100::tc_fence_after();
-      float sv[BN];
+      float sv[COLS];
 #pragma unroll
-      for (int c = 0; c < BN; c += 32)
-        sm100::tmem_ld32(tmem + lane_addr + sb * 128 + c, reinterpret_cast<uint32_t*>(sv + c));
+      for (int c = 0; c < COLS; c += 32)
+        sm100::tmem_ld32(tmem + lane_addr + sb * 128 + half * COLS + c, reinterpret_cast<uint32_t*>(sv + c));
       sm100::tmem_ld_wait();
       sm100::tc_fence_before();
       sm100::mbar_arrive(&bars->s_empty[sb]);
-      const int k0 = t * BN;
+      const int k0 = t * BN + half * COLS;
       float mx = -INFINITY;
-      if (k0 + BN - 1 <= cached + q_lo && k0 + BN <= kv_end) {
+      if (t * BN + BN - 1 <= cached + q_lo && t * BN + BN <= kv_end) {
 #pragma unroll
-        for (int j = 0; j < BN; ++j) {
+        for (int j = 0; j < COLS; ++j) {
           sv[j] *= scale_log2;
           mx = fmaxf(mx, sv[j]);
         }
       } else {
 #pragma unroll
-        for (int j = 0; j < BN; ++j) {
+        for (int j = 0; j < COLS; ++j) {
           sv[j] = (k0 + j <= limit) ? sv[j] * scale_log2 : -INFINITY;
           mx = fmaxf(mx, sv[j]);
         }
+      }
+      if (WG == 2) {                                   // row maximum over both halves
+        xch[(t & 1) * 256 + half * 128 + r] = mx;
+        pair_bar();
+        mx = fmaxf(mx, xch[(t & 1) * 256 + (half ^ 1) * 128 + r]);
       }
       // lazy rescaling: keep the old reference maximum unless this tile exceeds it by 2^8
       const bool grow = mx > m + RESCALE_LOG2;           // also true for the first finite tile
@@ -254,20 +268,17 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         const float m_new = grow ? mx : m;
         const float f = (m == -INFINITY) ? 0.f : exp2f(m - m_new);
         if (t > 0) {
-          if (!sm100::mbar_wait(&bars->pv_done, (uint32_t)(t - 1) & 1u)) {
-            ok = false;
-            break;
-          }
+          if (ok && !sm100::mbar_wait(&bars->pv_done, (uint32_t)(t - 1) & 1u)) ok = false;
           waited = true;
           sm100::tc_fence_after();
 #pragma unroll 1
-          for (int c = 0; c < HD; c += 16) {
+          for (int c = 0; c < HD / WG; c += 16) {
             uint32_t o[16];
-            sm100::tmem_ld16(tmem_o + lane_addr + c, o);
+            sm100::tmem_ld16(tmem_o + lane_addr + half * (HD / WG) + c, o);
             sm100::tmem_ld_wait();
 #pragma unroll
             for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * f);
-            sm100::tmem_st16(tmem_o + lane_addr + c, o);
+            sm100::tmem_st16(tmem_o + lane_addr + half * (HD / WG) + c, o);
           }
           sm100::tmem_st_wait();
           l *= f;
@@ -276,24 +287,19 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       }
       const float mref = (m == -INFINITY) ? 0.f : m;
       float rs = 0.f;
-      uint32_t pk[BN / 2];
+      uint32_t pk[COLS / 2];
 #pragma unroll
-      for (int j = 0; j < BN; j += 2) {
+      for (int j = 0; j < COLS; j += 2) {
         const float p0 = exp2f(sv[j] - mref), p1 = exp2f(sv[j + 1] - mref);
         rs += p0 + p1;
         pk[j >> 1] = pack_bf2(p0, p1);
       }
-      l += rs;
-      if (t > 0 && !waited) {
-        if (!sm100::mbar_wait(&bars->pv_done, (uint32_t)(t - 1) & 1u)) {
-          ok = false;
-          break;
-        }
-      }
-      // P row r: two 64-key chunks, 16-byte pieces XOR-swizzled by (r & 7) like a TMA tile
+      l += rs;                                         // with WG == 2: this half's share of the row sum
+      if (t > 0 && !waited && ok && !sm100::mbar_wait(&bars->pv_done, (uint32_t)(t - 1) & 1u)) ok = false;
+      // P row r: 64-key chunks, 16-byte pieces XOR-swizzled by (r & 7) like a TMA tile
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint8_t* row = p_s + c * CHUNK_BYTES + r * 128;
+      for (int c = 0; c < COLS / 64; ++c) {
+        uint8_t* row = p_s + (half * (COLS / 64) + c) * CHUNK_BYTES + r * 128;
 #pragma unroll
         for (int piece = 0; piece < 8; ++piece) {
           const int i = c * 32 + piece * 4;
@@ -308,15 +314,20 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     if (ok && !sm100::mbar_wait(&bars->pv_done, (uint32_t)(ntiles - 1) & 1u)) ok = false;
     if (!ok && lane == 0) atomicOr(status, GV_ST_TIMEOUT_EPI);
     sm100::tc_fence_after();
+    if (WG == 2) {                                     // row sum over both halves
+      xch[512 + half * 128 + r] = l;
+      pair_bar();
+      l += xch[512 + (half ^ 1) * 128 + r];
+    }
     if (__all_sync(0xffffffffu, ok)) {
       // rows past the end of the request take part in the (warp-collective) TMEM loads too
       const bool live = qi < qlen;
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      bf16* orow = out + ((long long)(qs0 + (live ? qi : 0)) * nq + h) * HD;
+      bf16* orow = out + ((long long)(qs0 + (live ? qi : 0)) * nq + h) * HD + half * (HD / WG);
 #pragma unroll 1
-      for (int c = 0; c < HD; c += 16) {
+      for (int c = 0; c < HD / WG; c += 16) {
         uint32_t o[16];
-        sm100::tmem_ld16(tmem_o + lane_addr + c, o);
+        sm100::tmem_ld16(tmem_o + lane_addr + half * (HD / WG) + c, o);
         sm100::tmem_ld_wait();
         float f[16];
 #pragma unroll
@@ -340,6 +351,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 }  // namespace gv
 
 using namespace gv;
+
+// Softmax warp groups of the tcgen05 prefill attention kernel: 1 (one thread per query row) or 2
+// (two threads per row, one 64-key half each).
+static long long g_prefill_tc_wg = 2;
+extern "C" void gv_set_prefill_tc_warpgroups(long long wg) { g_prefill_tc_wg = wg == 2 ? 2 : 1; }
 
 // Same arguments as gv_paged_attention_prefill plus `total_tokens` (rows of q / out). head_dim
 // must be 128 and block_size a power of two in [8, ...] that divides or is a multiple of 128;
@@ -369,10 +385,13 @@ extern "C" int gv_paged_attention_prefill_tc(const void* q, const void* k_cache,
   if ((rc = gemm::cached_tmap_bf16(&tmQ, q, total_tokens, nq * 128, nq * 128, 128)) != GV_OK) return rc;
   if ((rc = gemm::cached_tmap_bf16(&tmK, k_cache, kv_rows, nkv * 128, nkv * 128, box)) != GV_OK) return rc;
   if ((rc = gemm::cached_tmap_bf16(&tmV, v_cache, kv_rows, nkv * 128, nkv * 128, box)) != GV_OK) return rc;
-  auto kern = fa::prefill_tc_kernel;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, fa::SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(fa::prefill_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         fa::SMEM_BYTES);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(fa::prefill_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               fa::SMEM_BYTES);
     if (e != cudaSuccess) {
       set_last_error("prefill_tc: smem attr", e);
       return GV_ECUDA;
@@ -380,9 +399,15 @@ extern "C" int gv_paged_attention_prefill_tc(const void* q, const void* k_cache,
     configured = true;
   }
   dim3 grid((unsigned)((max_q_len + fa::BM - 1) / fa::BM), (unsigned)nq, (unsigned)batch);
-  kern<<<grid, fa::THREADS, fa::SMEM_BYTES, (cudaStream_t)stream>>>(
-      tmQ, tmK, tmV, (const int*)block_tables, (const int*)q_start, (const int*)cached_lens, (bf16*)out,
-      (int)nq, (int)nkv, (int)block_size, (int)max_blocks, scale * 1.4426950408889634f, num_blocks,
-      status_word());
+  if (g_prefill_tc_wg == 2)
+    fa::prefill_tc_kernel<2><<<grid, 64 + 256, fa::SMEM_BYTES, (cudaStream_t)stream>>>(
+        tmQ, tmK, tmV, (const int*)block_tables, (const int*)q_start, (const int*)cached_lens, (bf16*)out,
+        (int)nq, (int)nkv, (int)block_size, (int)max_blocks, scale * 1.4426950408889634f, num_blocks,
+        status_word());
+  else
+    fa::prefill_tc_kernel<1><<<grid, 64 + 128, fa::SMEM_BYTES, (cudaStream_t)stream>>>(
+        tmQ, tmK, tmV, (const int*)block_tables, (const int*)q_start, (const int*)cached_lens, (bf16*)out,
+        (int)nq, (int)nkv, (int)block_size, (int)max_blocks, scale * 1.4426950408889634f, num_blocks,
+        status_word());
   return check_launch("paged_prefill_tc");
 }

@@ -86,6 +86,8 @@ int gv_paged_attention_decode_merged(const void* q, const void* k_cache, const v
                                      long long nq, long long nkv, long long head_dim,
                                      long long block_size, long long max_blocks, long long nsplit,
                                      float scale, long long num_blocks, void* stream);
+// Softmax warp groups of that kernel: 1 = one thread per query row, 2 (default) = two per row.
+void gv_set_prefill_tc_warpgroups(long long wg);
 // tcgen05 / TMEM / TMA flash attention for head_dim 128 (attention_prefill_tc.cu).
 int gv_paged_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache,
                                   const void* block_tables, const void* q_start,

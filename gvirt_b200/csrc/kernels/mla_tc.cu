@@ -217,13 +217,12 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
     float m = -INFINITY, l = 0.f;
     bool ok = true;
-    for (int t = 0; t < ntiles && ok; ++t) {
+    // A wait that runs out only clears `ok`: the thread keeps walking the loop without further
+    // waits, so the warp-collective TMEM accesses below always see the whole warp.
+    for (int t = 0; t < ntiles; ++t) {
       const int sb = t & 1;
       const uint32_t sph = (uint32_t)(t >> 1) & 1u;
-      if (!sm100::mbar_wait(&bars->s_full[sb], sph)) {
-        ok = false;
-        break;
-      }
+      if (ok && !sm100::mbar_wait(&bars->s_full[sb], sph)) ok = false;
       sm100::tc_fence_after();
       float sv[BN];
       sm100::tmem_ld32(tmem + lane_addr + sb * 32, reinterpret_cast<uint32_t*>(sv));
@@ -244,10 +243,7 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         const float m_new = grow ? mx : m;
         const float f = (m == -INFINITY) ? 0.f : exp2f(m - m_new);
         if (t > 0) {
-          if (!sm100::mbar_wait(&bars->pv_done, (uint32_t)(t - 1) & 1u)) {
-            ok = false;
-            break;
-          }
+          if (ok && !sm100::mbar_wait(&bars->pv_done, (uint32_t)(t - 1) & 1u)) ok = false;
           waited = true;
           sm100::tc_fence_after();
 #pragma unroll 1
@@ -274,12 +270,7 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         pk[j >> 1] = pack_bf2(p0, p1);
       }
       l += rs;
-      if (t > 0 && !waited) {
-        if (!sm100::mbar_wait(&bars->pv_done, (uint32_t)(t - 1) & 1u)) {
-          ok = false;
-          break;
-        }
-      }
+      if (t > 0 && !waited && ok && !sm100::mbar_wait(&bars->pv_done, (uint32_t)(t - 1) & 1u)) ok = false;
       // P row r: 64 bytes = 4 pieces of 16 bytes, XOR-swizzled by ((r >> 1) & 3) (64-byte swizzle)
       uint8_t* row = p_s + r * 64;
 #pragma unroll

@@ -219,12 +219,16 @@ class Transformer:
             ws.put(tmp)
             return tiles
         heap = ctx.symm
-        if heap is not None and a.is_cuda and heap.can_fuse_gemm_ar(a, w):
+        fusable = heap is not None and a.is_cuda and heap.can_fuse_gemm_ar(a, w)
+        if fusable and flags().fused_ar_residual:
             heap.gemm_allreduce(a, w, out=x, residual=x, ss_out=ss, next_w=next_w)
             return tiles
         tmp = ws.get(tuple(x.shape), self.dtype)
-        F.linear(a, w, None, out=tmp)
-        coll.all_reduce(tmp, ctx.tp_group, ctx)
+        if fusable:
+            heap.gemm_allreduce(a, w, out=tmp)          # GEMM + all-reduce in one kernel, add behind it
+        else:
+            F.linear(a, w, None, out=tmp)
+            coll.all_reduce(tmp, ctx.tp_group, ctx)
         D.add_residual_sumsq(tmp, x, ss)
         ws.put(tmp)
         return 1

@@ -150,6 +150,15 @@ def run_floor(cfg, ctx, B, P, K, W, advance=0):
     barrier()
     e2e_s = time.perf_counter() - t0
     nxt = host_tok.to(dev)
+    import os
+    if os.environ.get("GVIRT_FLOOR_PROFILE") and ctx.rank == 0:
+        # where the eager step spends its time (debug aid: prints the top operators of two steps)
+        from torch.profiler import ProfilerActivity, profile
+        with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA]) as prof:
+            for _ in range(2):
+                model.forward(nxt[:, None], pos)
+            torch.cuda.synchronize()
+        print(prof.key_averages().table(sort_by="cuda_time_total", row_limit=18), flush=True)
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     ev0.record()

@@ -15,12 +15,21 @@ from tests.test_gpu_attention import build
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
+DEFAULT_WG = 2
 
 
-def _tc(q, kc, vc, m, nq, nkv, hd, bs):
+def _tc(q, kc, vc, m, nq, nkv, hd, bs, wg=None):
+    """`wg`: softmax warp groups of the kernel (1 or 2); None keeps the library default."""
     out = torch.empty_like(q)
-    _native.call("paged_attention_prefill_tc", q, kc, vc, m.block_tables, m.query_start_loc, m.cached_lens, out,
-                 q.shape[0], m.batch, m.max_q_len, nq, nkv, hd, bs, m.block_tables.shape[1], 1.0, kc.shape[0])
+    lib = _native.kernels()
+    if wg is not None:
+        lib.gv_set_prefill_tc_warpgroups(wg)
+    try:
+        _native.call("paged_attention_prefill_tc", q, kc, vc, m.block_tables, m.query_start_loc, m.cached_lens, out,
+                     q.shape[0], m.batch, m.max_q_len, nq, nkv, hd, bs, m.block_tables.shape[1], 1.0, kc.shape[0])
+    finally:
+        if wg is not None:
+            lib.gv_set_prefill_tc_warpgroups(DEFAULT_WG)
     return out
 
 
@@ -57,8 +66,9 @@ def test_prefill_tc_block_sizes_and_groups(bs, nq, nkv):
     cached = [0, 0, 5, 130, 0, 900, 64]
     q, kc, vc, mc, m = build(lens, cached, nq, nkv, hd, bs, seed=bs + nq)
     want = ref.paged_attention(q, kc, vc, mc.block_tables, mc.query_start_loc, mc.cached_lens, nq, nkv, hd, bs)
-    got = _tc(q.to(DEV), kc.to(DEV), vc.to(DEV), m, nq, nkv, hd, bs)
-    close(got, want, atol=1e-2, rtol=2e-2, what=f"prefill tc bs={bs} {nq}/{nkv}")
+    for wg in (1, 2):
+        got = _tc(q.to(DEV), kc.to(DEV), vc.to(DEV), m, nq, nkv, hd, bs, wg=wg)
+        close(got, want, atol=1e-2, rtol=2e-2, what=f"prefill tc bs={bs} {nq}/{nkv} warp groups={wg}")
     status_ok()
 
 
@@ -77,8 +87,9 @@ def test_prefill_tc_forces_lazy_rescale_of_the_output():
             kc[blk] = (kc[blk].float() * (0.2 + pos / 40.0)[:, None, None]).bfloat16()
     q = (q.float() * 3).bfloat16()
     want = ref.paged_attention(q, kc, vc, mc.block_tables, mc.query_start_loc, mc.cached_lens, nq, nkv, hd, bs)
-    got = _tc(q.to(DEV), kc.to(DEV), vc.to(DEV), m, nq, nkv, hd, bs)
-    close(got, want, atol=2e-2, rtol=2e-2, what="prefill tc with rescaling")
+    for wg in (1, 2):
+        got = _tc(q.to(DEV), kc.to(DEV), vc.to(DEV), m, nq, nkv, hd, bs, wg=wg)
+        close(got, want, atol=2e-2, rtol=2e-2, what=f"prefill tc with rescaling, warp groups={wg}")
     status_ok()
 
 
@@ -102,8 +113,9 @@ def test_prefill_tc_32769_tokens():
     nq, nkv, hd, bs = 2, 1, 128, 128
     q, kc, vc, mc, m = build([32769], [0], nq, nkv, hd, bs, seed=2)
     want = _ref_gpu(q, kc, vc, mc, nq, nkv, hd, bs)
-    got = _tc(q.to(DEV), kc.to(DEV), vc.to(DEV), m, nq, nkv, hd, bs)
-    close(got, want, atol=1e-2, rtol=2e-2, what="32769-token prefill")
+    for wg in (1, 2):
+        got = _tc(q.to(DEV), kc.to(DEV), vc.to(DEV), m, nq, nkv, hd, bs, wg=wg)
+        close(got, want, atol=1e-2, rtol=2e-2, what=f"32769-token prefill, warp groups={wg}")
     status_ok()
 
 

@@ -75,6 +75,27 @@ def test_gemm_allreduce_single_rank(M, N, K):
     status_ok()
 
 
+@pytest.mark.parametrize("M,N,K", [(64, 4096, 1024), (1, 512, 256), (100, 1024, 3584), (128, 2048, 512)])
+def test_gemm_allreduce_residual_in_place_and_sumsq_single_rank(M, N, K):
+    """The producer form used by the fused decode loop: the residual stream is updated in place and
+    the sums of squares of the new rows are left per 128-feature tile."""
+    heap = _heap()
+    g = torch.Generator(device=DEV).manual_seed(1)
+    x = (torch.randn(M, K, device=DEV, generator=g) * 0.5).bfloat16()
+    w = (torch.randn(N, K, device=DEV, generator=g) * 0.05).bfloat16()
+    res = torch.randn(M, N, device=DEV, generator=g).bfloat16()
+    want = x.float() @ w.float().t() + res.float()
+    for rep in range(2):
+        xs = res.clone()
+        ss = torch.full((128, N // 128), -1.0, device=DEV)
+        heap.gemm_allreduce(x, w, out=xs, residual=xs, ss_out=ss)
+        close(xs, want, atol=6e-2, rtol=2e-2, what=f"in-place residual rep {rep}")
+        want_ss = xs.float().reshape(M, N // 128, 128).pow(2).sum(-1)
+        close(ss[:M], want_ss, atol=1e-3, rtol=1e-4, what="tile sums of squares")
+        assert (ss[M:] == -1).all()
+    status_ok()
+
+
 def test_gemm_allreduce_in_cuda_graph():
     heap = _heap()
     x = (torch.randn(32, 1024, device=DEV) * 0.5).bfloat16()
