@@ -122,16 +122,12 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     float r[4];          // EPI_RESID: residual row; EPI_ROPE: cos
     float sn[4];         // EPI_ROPE: sin
     int slot;            // EPI_ROPE: cache slot of k / v heads
-    float scale;         // RMSNorm factor of the token (1 without ss_in)
   };
   auto load_side = [&](int c, long long pos, int slot, Side& sd) {
     sd.slot = slot;
-    sd.scale = 0.f;
 #pragma unroll
     for (int j = 0; j < 4; ++j) sd.r[j] = sd.sn[j] = 0.f;
     if (c >= M) return;
-    if (e.ss_in != nullptr)
-      for (int t = lane; t < e.ss_tiles; t += 32) sd.scale += e.ss_in[(long long)c * e.ss_ld + t];
     if (MODE == EPI_RESID) {
       if (p_ok) unpack4f(*reinterpret_cast<const uint2*>(e.residual + (long long)c * ldo + p), sd.r);
     } else if (MODE == EPI_ROPE) {
@@ -148,21 +144,33 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       }
     }
   };
-  auto finish_side = [&](Side& sd) {     // every lane of the warp calls it
-    sd.scale = e.ss_in != nullptr ? rsqrtf(warp_sum(sd.scale) * e.inv_h + e.eps) : 1.f;
-  };
   constexpr int NPRE = 4;
   Side pre[NPRE];
   float b4[4] = {0.f, 0.f, 0.f, 0.f};
+  // RMSNorm factor of the warp's i-th column, held by lane i (a warp owns at most BN / 4 <= 32
+  // columns): each lane sums the partial sums of squares of one token, all lanes at once, so the
+  // factors of every column cost one round of memory latency, hidden behind the main loop.
+  float my_scale = 1.f;
+  __shared__ float s_scale[BN];                        // EPI_SWIGLU: the factors, by column index
   if (warp >= 2) {
     if (e.bias != nullptr && p_ok) unpack4f(*reinterpret_cast<const uint2*>(e.bias + p), b4);
+    if (e.ss_in != nullptr) {
+      const int ci = ew + 4 * lane;
+      const int c = z + ci * splitk;
+      if (ci < ncols && c < M) {
+        const float* row = e.ss_in + (long long)c * e.ss_ld;
+        float acc = 0.f;
+#pragma unroll 8
+        for (int t = 0; t < e.ss_tiles; ++t) acc += row[t];
+        my_scale = rsqrtf(acc * e.inv_h + e.eps);
+      }
+    }
+    if (MODE == EPI_SWIGLU && ew + 4 * lane < BN) s_scale[ew + 4 * lane] = my_scale;
 #pragma unroll
     for (int i = 0; i < NPRE; ++i) {
       const int ci = ew + 4 * i;
       load_side(ci < ncols ? z + ci * splitk : M, pos_pre[i], slot_pre[i], pre[i]);
     }
-#pragma unroll
-    for (int i = 0; i < NPRE; ++i) finish_side(pre[i]);
     wait_accum(sh, status);
 #pragma unroll 1
     for (int c = 0; c < BN; c += 16) {
@@ -175,9 +183,39 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   }
   if (splitk > 1) cluster_sync_all();
   else __syncthreads();
-  if (warp >= 2) {
+  if (MODE == EPI_SWIGLU && warp >= 2) {
+    // Rows 0..63 of the tile are the gate rows of 64 features, rows 64..127 the up rows of the
+    // same features: one item = 4 features of one token, all 128 threads busy.
+    const int et = threadIdx.x - 64;
+    const int half = N >> 1;
+    for (int idx = et; idx < ncols * 16; idx += 128) {
+      const int ci = idx >> 4;
+      const int c = z + ci * splitk;
+      const int f4 = (idx & 15) * 4;
+      const int f = (p0 >> 1) + f4;
+      if (c >= M || f + 4 > half) continue;
+      float4 g4, u4;
+      if (splitk > 1) {
+        g4 = cluster_sum4(&red[c * BM + f4], splitk);
+        u4 = cluster_sum4(&red[c * BM + 64 + f4], splitk);
+      } else {
+        g4 = *reinterpret_cast<const float4*>(&red[c * BM + f4]);
+        u4 = *reinterpret_cast<const float4*>(&red[c * BM + 64 + f4]);
+      }
+      const float sc = s_scale[ci];
+      const float g[4] = {g4.x, g4.y, g4.z, g4.w}, u[4] = {u4.x, u4.y, u4.z, u4.w};
+      float o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        // the unfused pair rounds the GEMM output to bf16 before activating: do the same
+        const float gj = rbf(g[j] * sc), uj = rbf(u[j] * sc);
+        o[j] = gj / (1.f + __expf(-gj)) * uj;
+      }
+      *reinterpret_cast<uint2*>(out + (long long)c * ldo + f) = pack4f(o);
+    }
+  } else if (warp >= 2) {
     // One token column: 32 lanes x 4 consecutive features = the 128 lanes of the tile.
-    auto column = [&](int c, const Side& sd) {
+    auto column = [&](int c, const Side& sd, float sc) {
       float a[4];
       if (splitk > 1) {
         const float4 t = cluster_sum4(&red[c * BM + r4], splitk);
@@ -186,7 +224,6 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         const float4 t = *reinterpret_cast<const float4*>(&red[c * BM + r4]);
         a[0] = t.x; a[1] = t.y; a[2] = t.z; a[3] = t.w;
       }
-      const float sc = sd.scale;
       if (MODE == EPI_PLAIN) {
         if (p_ok) {
           float o[4];
@@ -194,18 +231,6 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           for (int j = 0; j < 4; ++j) o[j] = a[j] * sc + b4[j];
           *reinterpret_cast<uint2*>(out + (long long)c * ldo + p) = pack4f(o);
         }
-      } else if (MODE == EPI_SWIGLU) {
-        // lanes 0..15 hold the gate rows of 64 features, lanes 16..31 the up rows of the same
-        float g[4], u[4], o[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          g[j] = rbf(a[j] * sc);       // the unfused pair rounds the GEMM output before activating
-          u[j] = __shfl_xor_sync(0xffffffffu, g[j], 16);
-          o[j] = g[j] / (1.f + __expf(-g[j])) * u[j];
-        }
-        const int f = (p0 >> 1) + r4;
-        if (lane < 16 && f + 4 <= (N >> 1))
-          *reinterpret_cast<uint2*>(out + (long long)c * ldo + f) = pack4f(o);
       } else if (MODE == EPI_RESID) {
         float o[4] = {0.f, 0.f, 0.f, 0.f};
         if (p_ok) {
@@ -262,6 +287,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       }
     };
     // one copy of the column code (kernels this short are sensitive to their instruction footprint)
+    Side ahead;                                        // side inputs of the column after this one
 #pragma unroll 1
     for (int i = 0, ci = ew; ci < ncols; ++i, ci += 4) {
       const int c = z + ci * splitk;
@@ -273,16 +299,24 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         for (int k = 1; k < NPRE; ++k)
           if (i == k) sd = pre[k];
       } else {
-        long long pos = 0;
-        int slot = -1;
-        if (MODE == EPI_ROPE) {
-          if (kind != 2) pos = e.positions[c];
-          if (kind != 0) slot = e.slots[c];
-        }
-        load_side(c, pos, slot, sd);
-        finish_side(sd);
+        sd = ahead;
       }
-      column(c, sd);
+      if (MODE == EPI_RESID || MODE == EPI_ROPE) {
+        // columns past the prefetched ones: request the next column's inputs before this one's
+        // arithmetic, so only the first of them waits for memory
+        const int cn = c + 4 * splitk;
+        if (i + 1 >= NPRE && ci + 4 < ncols && cn < M) {
+          long long pos = 0;
+          int slot = -1;
+          if (MODE == EPI_ROPE) {
+            if (kind != 2) pos = e.positions[cn];
+            if (kind != 0) slot = e.slots[cn];
+          }
+          load_side(cn, pos, slot, ahead);
+        }
+      }
+      const float sc = __shfl_sync(0xffffffffu, my_scale, i);
+      column(c, sd, sc);
     }
   }
   if (splitk > 1) cluster_sync_all();  // peers may still be reading this CTA's shared memory

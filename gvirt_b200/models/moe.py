@@ -16,7 +16,11 @@ a bitmap; the expert-parallel exchange has two implementations:
 * *fused dispatch / combine* (``parallel.moe_a2a``; CUDA + symmetric heap): the routing
   kernel writes each (token, expert) row straight into the destination rank's receive region
   over NVLink, the grouped GEMM consumes expert-major segments, and the combine kernel pulls
-  the weighted rows back — no host synchronisation, no count-exchange collective.
+  the weighted rows back — no host synchronisation, no count-exchange collective. With
+  data-parallel attention every rank dispatches its own tokens; with tensor-parallel attention
+  (tokens replicated) rank r dispatches the r-th 1/tp slice of the tokens and the finished
+  slices are all-gathered, which replaces the all-reduce of ``[T, H]`` partial sums (each row
+  crosses the links once, already summed) and runs every routed row on one rank only.
 """
 from __future__ import annotations
 
@@ -48,12 +52,32 @@ def forward(model, li, lw, h, ws, out):
     T = h.shape[0]
     e_local = cfg.num_experts // ctx.ep
     e_start = ctx.ep_rank * e_local
-    weights, ids = route(model, lw, h)
 
     a2a = getattr(ctx, "moe_a2a", None)
-    if a2a is not None and h.is_cuda and flags().moe_alltoall and ctx.dp > 1 and a2a.supports(T):
+    a2a_ok = a2a is not None and flags().moe_alltoall and (h.is_cuda or getattr(a2a, "any_device", False))
+    if a2a_ok and ctx.dp == 1 and ctx.tp > 1 and ctx.ep == ctx.tp and a2a.supports(-(-T // ctx.tp)):
+        # tensor-parallel attention: the tokens are the same on every rank; this rank routes and
+        # dispatches its 1/tp slice, the slices of finished rows are gathered
+        tl = -(-T // ctx.tp)
+        lo = min(T, ctx.tp_rank * tl)
+        n = min(T, lo + tl) - lo
+        hs = h[lo:lo + n]
+        weights, ids = route(model, lw, hs)
+        mine = ws.get((tl, cfg.hidden_size), model.dtype)
+        a2a.forward(hs, weights, ids, lw, out=mine[:n], clamp=cfg.swiglu_clamp)
+        if tl * ctx.tp == T:
+            coll.all_gather(mine, ctx.tp_group, ctx, out=out)
+        else:
+            full = ws.get((tl * ctx.tp, cfg.hidden_size), model.dtype)
+            coll.all_gather(mine, ctx.tp_group, ctx, out=full)
+            out.copy_(full[:T])
+            ws.put(full)
+        ws.put(mine)
+        summed_over_ep = True
+        return _add_shared(model, lw, h, ws, out, summed_over_ep)
+    weights, ids = route(model, lw, h)
+    if a2a_ok and ctx.dp > 1 and a2a.supports(T):
         a2a.forward(h, weights, ids, lw, out=out, clamp=cfg.swiglu_clamp)
-        tokens_replicated = False
         summed_over_ep = True
     elif ctx.dp > 1 and ctx.ep > 1:
         # attention is data parallel: gather every DP rank's tokens, run local experts, scatter back
@@ -75,7 +99,13 @@ def forward(model, li, lw, h, ws, out):
                                 w13_scale=getattr(lw, "w13_scale", None),
                                 w2_scale=getattr(lw, "w2_scale", None))
         summed_over_ep = ctx.ep == 1
+    return _add_shared(model, lw, h, ws, out, summed_over_ep)
 
+
+def _add_shared(model, lw, h, ws, out, summed_over_ep):
+    """Shared expert and the reduction that is still owed over the EP / TP group."""
+    cfg, ctx = model.cfg, model.ctx
+    T = h.shape[0]
     # shared expert: partial sum on every TP rank (weights TP-sharded), joins the final reduce
     if getattr(lw, "ws_gate_up", None) is not None:
         sh = ws.get((T, cfg.hidden_size), model.dtype)

@@ -35,21 +35,25 @@ def a2a_bytes(cfg: ModelConfig, world: int, tokens_cap: int) -> int:
     return rows * (2 * H + 8 + (H // 128) * 4) + tokens_cap * K * H * 2 + (64 << 20)
 
 
-def fit_step_to_exchange(cfg: ModelConfig, world: int) -> int:
+def fit_step_to_exchange(cfg: ModelConfig, world: int, slices: int = 1) -> int:
     """Keep the fused MoE exchange exact: when the slot-addressed buffers behind the receive regions
     cannot hold the worst case of a full step (every token of every rank routed to one expert),
-    shrink the step (`cfg.max_num_batched_tokens`: prefill chunks get smaller) until they can. With
+    shrink the step (`cfg.max_num_batched_tokens`: prefill chunks get smaller) until they can.
+    `slices`: ranks that share one step's tokens (tensor-parallel attention: each dispatches
+    1/slices of them; 1 with data-parallel attention). With
     GVIRT_ACTIVE_TOKENS_RATIO_PER_EP < 1 the caller has asked for the approximate mode and nothing
     is changed. Returns the step size in force."""
     from .moe_a2a import a2a_exact_tokens
     if flags().active_tokens_ratio_per_ep < 1.0:
         return cfg.max_num_batched_tokens
-    exact = a2a_exact_tokens(cfg, world, cfg.max_num_batched_tokens)
-    if exact < cfg.max_num_batched_tokens:
-        if exact < cfg.max_batch_size:
+    per_rank = -(-cfg.max_num_batched_tokens // slices)
+    exact = a2a_exact_tokens(cfg, world, per_rank)
+    if exact < per_rank:
+        step = exact * slices
+        if step < cfg.max_batch_size:
             raise ValueError(f"the fused MoE exchange cannot hold a decode step of {cfg.max_batch_size} requests "
-                             f"exactly ({exact} tokens fit): raise GVIRT_A2A_SCRATCH_GB or lower max_batch_size")
-        cfg.max_num_batched_tokens = max(exact // 128 * 128, cfg.max_batch_size) if exact >= 128 else exact
+                             f"exactly ({step} tokens fit): raise GVIRT_A2A_SCRATCH_GB or lower max_batch_size")
+        cfg.max_num_batched_tokens = max(step // 128 * 128, cfg.max_batch_size) if step >= 128 else step
     return cfg.max_num_batched_tokens
 
 
@@ -58,10 +62,16 @@ def attach_device_comm(ctx, cfg: ModelConfig) -> None:
     if ctx.device.type != "cuda" or ctx.world == 1:
         return
     ep_bytes = 0
-    use_a2a = cfg.is_moe and ctx.dp > 1 and ctx.ep > 1 and flags().moe_alltoall
+    # the fused exchange serves data-parallel attention (every rank dispatches its own tokens) and
+    # tensor-parallel attention over the same ranks as the experts (every rank dispatches a 1/tp
+    # slice of the replicated tokens)
+    sliced = ctx.dp == 1 and ctx.tp > 1 and ctx.ep == ctx.tp
+    use_a2a = cfg.is_moe and ctx.ep > 1 and flags().moe_alltoall and (ctx.dp > 1 or sliced)
+    tokens_cap = cfg.max_num_batched_tokens
     if use_a2a:
-        fit_step_to_exchange(cfg, ctx.ep)
-        ep_bytes = a2a_bytes(cfg, ctx.ep, cfg.max_num_batched_tokens)
+        fit_step_to_exchange(cfg, ctx.ep, ctx.tp if sliced else 1)
+        tokens_cap = -(-cfg.max_num_batched_tokens // ctx.tp) if sliced else cfg.max_num_batched_tokens
+        ep_bytes = a2a_bytes(cfg, ctx.ep, tokens_cap)
     attach_symmetric_heap(ctx, nbytes=heap_bytes(cfg, ctx.tp) if ctx.tp > 1 else 0, ep_nbytes=ep_bytes)
     if use_a2a:
-        attach_moe_a2a(ctx, cfg, tokens_cap=cfg.max_num_batched_tokens)
+        attach_moe_a2a(ctx, cfg, tokens_cap=tokens_cap)

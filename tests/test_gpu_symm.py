@@ -162,7 +162,7 @@ def _run(mode, world):
     return run_workers(mode, world, timeout=900, extra_env={"NCCL_NVLS_ENABLE": "0"})
 
 
-@pytest.mark.parametrize("mode", ["collectives_gpu", "gemm_ar_gpu", "gemm_sp_gpu", "tp_model_gpu", "moe_a2a_gpu"])
+@pytest.mark.parametrize("mode", ["collectives_gpu", "gemm_ar_gpu", "gemm_sp_gpu", "tp_model_gpu", "moe_a2a_gpu", "moe_tp_slice_gpu"])
 def test_multi_gpu(mode):
     n = torch.cuda.device_count()
     if n < 2:
