@@ -29,12 +29,20 @@ constexpr int GG_MAX_SEGMENTS = 512;  // prefix table in static shared memory (2
 // column-tile counts, tile t = (column tile t / tilesN, weight-row tile t % tilesN). The operand
 // ring keeps running across tiles and the accumulator is double-buffered in TMEM, so the
 // epilogue of one tile overlaps the K loop of the next.
-template <int BN>
+//
+// SWIGLU: the weight holds gate and up rows interleaved in blocks of 32 = [16 gate | 16 up] rows of
+// the same 16 features, so that both halves of a feature sit in one TMEM quadrant, 16 lanes
+// apart: the epilogue warp pairs them with one shuffle and writes
+//     out[row, f] = silu(gate) * up        (out is [rows, N / 2])
+// without the [rows, N] intermediate ever reaching memory. `clamp` > 0 bounds gate from above and
+// up on both sides first (the reference's clamped SwiGLU).
+template <int BN, bool SWIGLU>
 __global__ void __launch_bounds__(NUM_THREADS, 2)
 grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW,
                          const __grid_constant__ CUtensorMap tmX, bf16* __restrict__ out,
                          const int* __restrict__ seg_start, const int* __restrict__ seg_end_arr, int N,
-                         int K, int G, int e_mod, long long ldo, int tilesN, unsigned int* status) {
+                         int K, int G, int e_mod, long long ldo, int tilesN, float clamp,
+                         unsigned int* status) {
   using C = Cfg<BN, 108>;
   constexpr int TCOLS = 2 * BN < 32 ? 32 : 2 * BN;
   extern __shared__ uint8_t smem_raw[];
@@ -179,7 +187,23 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW,
         uint32_t r[16];
         sm100::tmem_ld16(tmem_addr(tmem_base, quad, (int)(buf * BN) + c), r);
         sm100::tmem_ld_wait();
-        if (n < N) {
+        if (SWIGLU) {
+          const int f = (tl.p0 >> 1) + quad * 16 + (lane & 15);    // output feature of this lane pair
+          const bool writer = lane < 16 && f < (N >> 1);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            // the unfused pair rounds the GEMM output to bf16 before activating: do the same
+            float g = bf2f(f2bf(__uint_as_float(r[j])));
+            float u = __shfl_xor_sync(0xffffffffu, g, 16);            // lanes >= 16 hold the up rows
+            if (clamp > 0.f) {
+              g = fminf(g, clamp);
+              u = fminf(fmaxf(u, -clamp), clamp);
+            }
+            const int row = tl.q0 + c + j;
+            if (writer && row < tl.seg_end)
+              out[(long long)row * ldo + f] = f2bf(g / (1.f + __expf(-g)) * u);
+          }
+        } else if (n < N) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int row = tl.q0 + c + j;
@@ -200,12 +224,12 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW,
   }
 }
 
-template <int BN>
+template <int BN, bool SWIGLU>
 static int launch_grouped(const CUtensorMap& tmW, const CUtensorMap& tmX, bf16* out,
                           const int* seg_start, const int* seg_end, int G, int e_mod, int rows_cap, int N,
-                          int K, long long ldo, cudaStream_t st) {
+                          int K, long long ldo, float clamp, cudaStream_t st) {
   using C = Cfg<BN, 108>;
-  auto kern = grouped_gemm_bf16_kernel<BN>;
+  auto kern = grouped_gemm_bf16_kernel<BN, SWIGLU>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -223,7 +247,7 @@ static int launch_grouped(const CUtensorMap& tmW, const CUtensorMap& tmX, bf16* 
   const long long slots = 2LL * num_sms();
   if (grid > slots) grid = slots;
   launch_pdl(kern, dim3((unsigned)grid), dim3(NUM_THREADS), C::SMEM_BYTES, st,
-      tmW, tmX, out, seg_start, seg_end, N, K, G, e_mod, ldo, tilesN, status_word());
+      tmW, tmX, out, seg_start, seg_end, N, K, G, e_mod, ldo, tilesN, clamp, status_word());
   return check_launch("grouped_gemm_bf16");
 }
 
@@ -235,7 +259,8 @@ using namespace gv::gemm;
 
 static int grouped_bf16(const void* xs, const void* w, const int* seg_start, const int* seg_end,
                         long long G, long long e_mod, void* out, long long rows_cap, long long N,
-                        long long K, long long E, long long avg_rows, cudaStream_t st) {
+                        long long K, long long E, long long avg_rows, cudaStream_t st, bool swiglu = false,
+                        float clamp = 0.f) {
   // expert weights never move: encode their 3-D map once
   static std::mutex mu;
   static std::map<std::tuple<const void*, long long, long long, long long>, CUtensorMap> wmaps;
@@ -255,12 +280,19 @@ static int grouped_bf16(const void* xs, const void* w, const int* seg_start, con
   }
   const int bn = avg_rows <= 16 ? 16 : avg_rows <= 32 ? 32 : avg_rows <= 64 ? 64 : 128;
   if ((rc = cached_tmap_bf16(&tmX, xs, rows_cap, K, K, bn)) != GV_OK) return rc;
+  const long long ldo = swiglu ? N / 2 : N;
+#define GV_GG(BN_)                                                                                      \
+  return swiglu ? launch_grouped<BN_, true>(tmW, tmX, (bf16*)out, seg_start, seg_end, (int)G, (int)e_mod, \
+                                            (int)rows_cap, (int)N, (int)K, ldo, clamp, st)              \
+                : launch_grouped<BN_, false>(tmW, tmX, (bf16*)out, seg_start, seg_end, (int)G, (int)e_mod, \
+                                             (int)rows_cap, (int)N, (int)K, ldo, 0.f, st)
   switch (bn) {
-    case 16: return launch_grouped<16>(tmW, tmX, (bf16*)out, seg_start, seg_end, (int)G, (int)e_mod, (int)rows_cap, (int)N, (int)K, N, st);
-    case 32: return launch_grouped<32>(tmW, tmX, (bf16*)out, seg_start, seg_end, (int)G, (int)e_mod, (int)rows_cap, (int)N, (int)K, N, st);
-    case 64: return launch_grouped<64>(tmW, tmX, (bf16*)out, seg_start, seg_end, (int)G, (int)e_mod, (int)rows_cap, (int)N, (int)K, N, st);
-    default: return launch_grouped<128>(tmW, tmX, (bf16*)out, seg_start, seg_end, (int)G, (int)e_mod, (int)rows_cap, (int)N, (int)K, N, st);
+    case 16: GV_GG(16);
+    case 32: GV_GG(32);
+    case 64: GV_GG(64);
+    default: GV_GG(128);
   }
+#undef GV_GG
 }
 
 // xs [rows_cap, K] bf16 (expert-major rows), w [E, N, K] bf16, offsets int32 [E + 1] on device,
@@ -286,4 +318,28 @@ extern "C" int gv_grouped_gemm_bf16_seg(const void* xs, const void* w, const voi
   if (rows_cap == 0) return GV_OK;
   return grouped_bf16(xs, w, (const int*)seg_start, (const int*)seg_end, G, E, out, rows_cap, N, K, E,
                       avg_rows, (cudaStream_t)stream);
+}
+
+// SwiGLU forms: w [E, N = 2 I, K] with rows interleaved in blocks of [16 gate | 16 up]
+// (N % 32 == 0), out [rows_cap, I] = silu(xs . gate^T) * (xs . up^T); `clamp` as in the kernel.
+extern "C" int gv_grouped_gemm_bf16_swiglu(const void* xs, const void* w, const void* offsets, void* out,
+                                           long long rows_cap, long long N, long long K, long long E,
+                                           float clamp, void* stream) {
+  if (!xs || !w || !offsets || !out || N <= 0 || K <= 0 || E <= 0) return GV_EINVAL;
+  if ((K & 7) || (N & 31)) return GV_EINVAL;
+  if (rows_cap == 0) return GV_OK;
+  const int* off = (const int*)offsets;
+  return grouped_bf16(xs, w, off, off + 1, E, 0, out, rows_cap, N, K, E, rows_cap / E, (cudaStream_t)stream,
+                      true, clamp);
+}
+
+extern "C" int gv_grouped_gemm_bf16_swiglu_seg(const void* xs, const void* w, const void* seg_start,
+                                               const void* seg_end, void* out, long long rows_cap,
+                                               long long N, long long K, long long E, long long G,
+                                               long long avg_rows, float clamp, void* stream) {
+  if (!xs || !w || !seg_start || !seg_end || !out || N <= 0 || K <= 0 || E <= 0 || G <= 0) return GV_EINVAL;
+  if ((K & 7) || (N & 31)) return GV_EINVAL;
+  if (rows_cap == 0) return GV_OK;
+  return grouped_bf16(xs, w, (const int*)seg_start, (const int*)seg_end, G, E, out, rows_cap, N, K, E,
+                      avg_rows, (cudaStream_t)stream, true, clamp);
 }

@@ -208,6 +208,14 @@ int gv_grouped_gemm_fp8(const void* xq, const void* x_scale, const void* wq, con
 int gv_grouped_gemm_bf16_seg(const void* xs, const void* w, const void* seg_start, const void* seg_end,
                              void* out, long long rows_cap, long long N, long long K, long long E,
                              long long G, long long avg_rows, void* stream);
+// SwiGLU in the epilogue: w rows interleaved in blocks of [16 gate | 16 up], out [rows_cap, N / 2]
+int gv_grouped_gemm_bf16_swiglu(const void* xs, const void* w, const void* offsets, void* out,
+                                long long rows_cap, long long N, long long K, long long E, float clamp,
+                                void* stream);
+int gv_grouped_gemm_bf16_swiglu_seg(const void* xs, const void* w, const void* seg_start,
+                                    const void* seg_end, void* out, long long rows_cap, long long N,
+                                    long long K, long long E, long long G, long long avg_rows, float clamp,
+                                    void* stream);
 int gv_grouped_gemm_fp8_seg(const void* xq, const void* x_scale, const void* wq, const void* w_scale,
                             const void* seg_start, const void* seg_end, void* out, long long rows_cap,
                             long long N, long long K, long long E, long long G, long long lds,

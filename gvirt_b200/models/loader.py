@@ -489,10 +489,14 @@ def save_hf_checkpoint(cfg: ModelConfig, weights: SimpleNamespace, path: str, sh
             t[m + "gate.weight"] = L.w_router
             if L.router_bias is not None:
                 t[m + "gate.e_score_correction_bias"] = L.router_bias
-            I = L.w13.shape[1] // 2
-            for e in range(L.w13.shape[0]):
-                t[f"{m}experts.{e}.gate_proj.weight"] = L.w13[e, :I]
-                t[f"{m}experts.{e}.up_proj.weight"] = L.w13[e, I:]
+            w13 = L.w13
+            if getattr(L, "w13_il16", False):   # device layout [16 gate | 16 up] blocks -> HF order
+                from ..ops.moe_ops import deinterleave16
+                w13 = deinterleave16(w13)
+            I = w13.shape[1] // 2
+            for e in range(w13.shape[0]):
+                t[f"{m}experts.{e}.gate_proj.weight"] = w13[e, :I]
+                t[f"{m}experts.{e}.up_proj.weight"] = w13[e, I:]
                 t[f"{m}experts.{e}.down_proj.weight"] = L.w2[e]
             if getattr(L, "ws_gate_up", None) is not None:
                 Is = L.ws_gate_up.shape[0] // 2

@@ -90,14 +90,14 @@ def forward(model, li, lw, h, ws, out):
         ig = coll.all_gather(ip, ctx.dp_group)
         yg = moe_ops.experts_forward(hg, wg, ig, lw.w13, lw.w2, e_start, cfg.swiglu_clamp,
                                      w13_scale=getattr(lw, "w13_scale", None),
-                                     w2_scale=getattr(lw, "w2_scale", None))
+                                     w2_scale=getattr(lw, "w2_scale", None), il16=getattr(lw, "w13_il16", False))
         y = coll.reduce_scatter(yg, ctx.dp_group)
         out.copy_(y[:T])
         summed_over_ep = True
     else:
         moe_ops.experts_forward(h, weights, ids, lw.w13, lw.w2, e_start, cfg.swiglu_clamp, out=out,
                                 w13_scale=getattr(lw, "w13_scale", None),
-                                w2_scale=getattr(lw, "w2_scale", None))
+                                w2_scale=getattr(lw, "w2_scale", None), il16=getattr(lw, "w13_il16", False))
         summed_over_ep = ctx.ep == 1
     return _add_shared(model, lw, h, ws, out, summed_over_ep)
 

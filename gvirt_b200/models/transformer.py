@@ -21,6 +21,7 @@ from ..config import AttnType, ModelConfig, flags
 from ..engine.arena import TorchWorkspace, Workspace
 from ..ops import decode_ops as D
 from ..ops import functional as F
+from ..ops import moe_ops
 from ..ops import reference as ref
 from ..parallel import collectives as coll
 from ..parallel import fused
@@ -66,11 +67,20 @@ class Transformer:
         does not change). Skipped for clamped SwiGLU, quantised weights and off the GPU
         (``force`` runs it anywhere: the CPU definition of the fused op takes the same layout)."""
         cfg = self.cfg
-        if cfg.swiglu_clamp > 0:
-            return
         if not force and (self.device.type != "cuda" or self.dtype != torch.bfloat16):
             return
         if not flags().fuse_swiglu:
+            return
+        # routed experts (bf16): gate / up rows in blocks of [16 gate | 16 up], the layout whose
+        # grouped GEMM applies SwiGLU (clamped or not) in its epilogue; marked ``w13_il16``
+        for lw in self.w.layers:
+            w13 = getattr(lw, "w13", None)
+            if (w13 is None or getattr(lw, "w13_il16", False) or w13.dtype != self.dtype
+                    or getattr(lw, "w13_scale", None) is not None or (w13.shape[1] // 2) % 16):
+                continue
+            lw.w13 = moe_ops.interleave16(w13)
+            lw.w13_il16 = True
+        if cfg.swiglu_clamp > 0:
             return
         for lw in self.w.layers:
             w = getattr(lw, "w_gate_up", None)

@@ -51,11 +51,46 @@ def _topk_cuda(logits, bias, k, mode, n_group, topk_group, renorm, route_scale):
     return w, ids
 
 
+def interleave16(w13: torch.Tensor) -> torch.Tensor:
+    """[E, 2 I, K] rows [gate (I) | up (I)] -> blocks of 32 rows = [16 gate | 16 up] of the same 16
+    features (I % 16 == 0): the layout whose grouped GEMM applies SwiGLU in its epilogue."""
+    E, N, K = w13.shape
+    I = N // 2
+    assert I % 16 == 0
+    g = w13[:, :I].reshape(E, I // 16, 16, K)
+    u = w13[:, I:].reshape(E, I // 16, 16, K)
+    return torch.cat([g, u], 2).reshape(E, N, K).contiguous()
+
+
+def deinterleave16(w13_il: torch.Tensor) -> torch.Tensor:
+    """Inverse of `interleave16`."""
+    E, N, K = w13_il.shape
+    b = w13_il.reshape(E, N // 32, 2, 16, K)
+    return torch.cat([b[:, :, 0].reshape(E, N // 2, K), b[:, :, 1].reshape(E, N // 2, K)], 1).contiguous()
+
+
+def grouped_gemm_swiglu(xs: torch.Tensor, w13_il: torch.Tensor, offsets: torch.Tensor, act: torch.Tensor,
+                        clamp: float = 0.0) -> torch.Tensor:
+    """act[r] = silu(xs[r] @ gate_e^T) * (xs[r] @ up_e^T) for rows r of expert e's segment, with
+    w13_il in the `interleave16` layout: the [rows, 2 I] intermediate is never written."""
+    E, N, K = w13_il.shape
+    if not xs.is_cuda:
+        gu = torch.zeros(xs.shape[0], N, dtype=xs.dtype)
+        grouped_gemm(xs, deinterleave16(w13_il), offsets, gu)
+        act.copy_(ref.silu_and_mul(gu, None, clamp))
+        return act
+    _native.call("grouped_gemm_bf16_swiglu", xs, w13_il, offsets, act, xs.shape[0], N, K, E, float(clamp))
+    return act
+
+
 def experts_forward(x, weights, ids, w13, w2, local_start=0, clamp=0.0, out=None,
-                    w13_scale=None, w2_scale=None):
+                    w13_scale=None, w2_scale=None, il16: bool = False):
     """y[t] = sum_k weights[t,k] * Expert_{ids[t,k]}(x[t]) over the experts held locally
-    (ids in [local_start, local_start + E_local)); other (token, k) pairs contribute zero."""
+    (ids in [local_start, local_start + E_local)); other (token, k) pairs contribute zero.
+    `il16`: w13 is in the `interleave16` layout (bf16 only)."""
     if not x.is_cuda:
+        if il16:
+            w13 = deinterleave16(w13)
         if w13_scale is not None:
             w13 = torch.stack([ref.dequant_fp8_block(w13[e], w13_scale[e]) for e in range(w13.shape[0])]).to(x.dtype)
             w2 = torch.stack([ref.dequant_fp8_block(w2[e], w2_scale[e]) for e in range(w2.shape[0])]).to(x.dtype)
@@ -77,10 +112,14 @@ def experts_forward(x, weights, ids, w13, w2, local_start=0, clamp=0.0, out=None
     xs = torch.empty(rows_cap, H, dtype=x.dtype, device=dev)
     _native.call("moe_permute", x, ids, counts, offsets, row_of, xs, T, H, K, E_local, local_start,
                  rows_cap)
-    gu = torch.empty(rows_cap, 2 * inter, dtype=x.dtype, device=dev)
-    grouped_gemm(xs, w13, offsets, gu, w_scale=w13_scale)
     act = torch.empty(rows_cap, inter, dtype=x.dtype, device=dev)
-    F.silu_and_mul(gu, out=act, num=offsets[E_local:], clamp=clamp)
+    if il16:
+        assert w13_scale is None
+        grouped_gemm_swiglu(xs, w13, offsets, act, clamp)
+    else:
+        gu = torch.empty(rows_cap, 2 * inter, dtype=x.dtype, device=dev)
+        grouped_gemm(xs, w13, offsets, gu, w_scale=w13_scale)
+        F.silu_and_mul(gu, out=act, num=offsets[E_local:], clamp=clamp)
     ys = torch.empty(rows_cap, H, dtype=x.dtype, device=dev)
     grouped_gemm(act, w2, offsets, ys, w_scale=w2_scale)
     if out is None:

@@ -118,8 +118,17 @@ class MoEA2A:
         # the other ranks run a similar step): decode steps get narrow tiles, so the padding rows of
         # the activation tile do not double the bytes streamed next to the weights
         avg_rows = max(1, int(self.R * max(T, 1) * self.K / max(self.cfg.num_experts, 1) + 0.5))
-        gu = self._buf("gu", (rows, 2 * inter), torch.bfloat16)
         w13s, w2s = getattr(lw, "w13_scale", None), getattr(lw, "w2_scale", None)
+        if getattr(lw, "w13_il16", False) and not self.fp8:
+            # gate / up rows interleaved: SwiGLU runs in the grouped GEMM's epilogue
+            act = self._buf("act", (rows, inter), torch.bfloat16)
+            ys = self._buf("ys", (rows, self.H), torch.bfloat16)
+            _native.call("grouped_gemm_bf16_swiglu_seg", self.xs, lw.w13, self.seg_start, self.seg_end, act, rows,
+                         2 * inter, self.H, E, E, avg_rows, float(clamp))
+            _native.call("grouped_gemm_bf16_seg", act, lw.w2, self.seg_start, self.seg_end, ys, rows, self.H,
+                         inter, E, E, avg_rows)
+            return self._combine(ys, peers, weights, row_of, out, T)
+        gu = self._buf("gu", (rows, 2 * inter), torch.bfloat16)
         if self.fp8:
             _native.call("grouped_gemm_fp8_seg", self.xs, self.xscale, lw.w13, w13s, self.seg_start, self.seg_end,
                          gu, rows, 2 * inter, self.H, E, E, rows, avg_rows)
@@ -150,6 +159,9 @@ class MoEA2A:
                 F.silu_and_mul(gu, out=act, clamp=clamp)
             _native.call("grouped_gemm_bf16_seg", act, lw.w2, self.seg_start, self.seg_end, ys, rows, self.H,
                          inter, E, E, avg_rows)
+        return self._combine(ys, peers, weights, row_of, out, T)
+
+    def _combine(self, ys, peers, weights, row_of, out, T):
         _native.call("moe_a2a_combine_push", ys, self.seg_end, peers, self.offs, self.state, self.dims)
         _native.call("moe_a2a_combine_wait", peers, self.offs, self.state, self.dims)
         if T > 0:

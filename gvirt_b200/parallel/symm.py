@@ -301,10 +301,14 @@ def attach_symmetric_heap(ctx, nbytes: int = 1 << 30, ep_nbytes: int = 0) -> Non
         nbytes = 0
     if not group_is_single_node(ctx.ep_ranks(), dpn):
         ep_nbytes = 0
+    shared = (ctx.tp > 1 and nbytes > 0 and ctx.ep > 1 and ep_nbytes > 0
+              and (ctx.ep_group is ctx.tp_group or ctx.ep == ctx.tp))
     if ctx.tp > 1 and nbytes > 0:
-        ctx.symm = SymmetricHeap(ctx.tp_group, ctx.tp_rank, ctx.tp, ctx.device, nbytes)
+        # experts spread over the same ranks as the tensor-parallel group: one heap serves both
+        ctx.symm = SymmetricHeap(ctx.tp_group, ctx.tp_rank, ctx.tp, ctx.device,
+                                 nbytes + (ep_nbytes if shared else 0))
     if ctx.ep > 1 and ep_nbytes > 0:
-        if ctx.ep_group is ctx.tp_group or (ctx.ep == ctx.tp and ctx.symm is not None):
+        if shared:
             ctx.symm_ep = ctx.symm
         else:
             ctx.symm_ep = SymmetricHeap(ctx.ep_group, ctx.ep_rank, ctx.ep, ctx.device, ep_nbytes)

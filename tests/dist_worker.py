@@ -518,7 +518,8 @@ def mode_tp_model_gpu(world):
         seen = []
         orig = llm.model.compute_logits
         llm.model.compute_logits = lambda hidden, meta, ws=None, batch=None: (
-            lambda lg: (seen.append(lg.detach().float().cpu()) if lg.device.type != "meta" else None, lg)[1])(
+            lambda lg: (seen.append(lg.detach().float().cpu())
+                        if lg.device.type != "meta" and not torch.cuda.is_current_stream_capturing() else None, lg)[1])(
                 orig(hidden, meta, ws, batch))
         return llm, [o.output for o in llm.generate(prompts, sp)], seen
 

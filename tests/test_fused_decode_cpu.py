@@ -128,3 +128,59 @@ def test_folded_model_matches_plain_model_and_saves_original_weights(tmp_path, k
     for a, b in zip(w_back.layers, w_plain.layers):
         assert torch.allclose(a.w_qkv, b.w_qkv, atol=1e-6) and torch.allclose(a.w_gate_up, b.w_gate_up, atol=1e-6)
         assert torch.equal(a.attn_norm, b.attn_norm) and torch.equal(a.mlp_norm, b.mlp_norm)
+
+
+def test_interleave16_round_trip_and_cpu_definition():
+    """Expert gate / up rows in blocks of [16 gate | 16 up]: the permutation inverts exactly and the
+    CPU definition of the fused grouped GEMM equals GEMM -> SwiGLU on the original order."""
+    import torch
+    from gvirt_b200.ops import moe_ops
+    from gvirt_b200.ops import reference as ref
+    g = torch.Generator().manual_seed(0)
+    E, I, K = 3, 48, 32
+    w13 = torch.randn(E, 2 * I, K, generator=g)
+    il = moe_ops.interleave16(w13)
+    assert torch.equal(moe_ops.deinterleave16(il), w13)
+    # block b of 32 rows = gate rows 16 b .. 16 b + 15, then up rows 16 b .. 16 b + 15
+    assert torch.equal(il[:, 32:48], w13[:, 16:32]) and torch.equal(il[:, 48:64], w13[:, I + 16:I + 32])
+    xs = torch.randn(10, K, generator=g)
+    off = torch.tensor([0, 4, 4, 10], dtype=torch.int32)
+    act = torch.zeros(10, I)
+    moe_ops.grouped_gemm_swiglu(xs, il, off, act, clamp=0.7)
+    gu = torch.zeros(10, 2 * I)
+    moe_ops.grouped_gemm(xs, w13, off, gu)
+    assert torch.allclose(act, ref.silu_and_mul(gu, None, 0.7))
+    T = 6
+    wts = torch.rand(T, 2, generator=g)
+    ids = torch.tensor([[0, 1], [2, 0], [1, 2], [0, 2], [1, 0], [2, 1]], dtype=torch.int32)
+    x = torch.randn(T, K, generator=g)
+    w2 = torch.randn(E, K, I, generator=g)
+    a = moe_ops.experts_forward(x, wts, ids, il, w2, 0, 0.0, il16=True)
+    b = moe_ops.experts_forward(x, wts, ids, w13, w2, 0, 0.0)
+    assert torch.allclose(a, b)
+
+
+def test_moe_model_with_interleaved_expert_rows_matches_and_saves_original_weights(tmp_path):
+    """A tiny MoE model whose expert gate / up rows were re-ordered for the fused grouped GEMM samples
+    the same tokens as the plain one, and a checkpoint written from it holds the original rows."""
+    kw = dict(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32, swiglu_clamp=2.0)
+    cfg = tiny_cfg(**kw)
+    ctx = ParallelContext()
+    w_plain = W.init_random(cfg, ctx, seed=8, device="cpu")
+    w_il = copy.deepcopy(w_plain)
+    m_plain, m_il = Transformer(cfg, w_plain, ctx), Transformer(cfg, w_il, ctx)
+    m_il._prepare_device_layouts(force=True)
+    moe_layers = [lw for lw in w_il.layers if getattr(lw, "w13", None) is not None]
+    assert moe_layers and all(getattr(lw, "w13_il16", False) for lw in moe_layers)
+    assert not torch.equal(moe_layers[0].w13, [lw for lw in w_plain.layers if getattr(lw, "w13", None) is not None][0].w13)
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(1, cfg.vocab_size, (n,), generator=g).tolist() for n in (9, 4)]
+    sp = SamplingParams(max_tokens=5, ignore_eos=True)
+    a = [o.output for o in LLM(m_plain).generate(prompts, sp)]
+    b = [o.output for o in LLM(m_il).generate(prompts, sp)]
+    assert a == b
+    loader.save_hf_checkpoint(cfg, w_il, str(tmp_path))
+    _, w_back, _, _ = loader.load_pretrained(str(tmp_path), ctx, device="cpu", dtype="float32")
+    for l0, l1 in zip(w_plain.layers, w_back.layers):
+        if getattr(l0, "w13", None) is not None:
+            assert torch.equal(l0.w13, l1.w13)

@@ -87,3 +87,24 @@ def test_experts_forward(local):
     want = ref.moe_ffn(x.cpu(), wts.cpu(), ids.cpu(), w13[start:start + e_local].cpu(), w2[start:start + e_local].cpu(), start)
     close(y, want, atol=2e-2, rtol=3e-2, what="experts_forward")
     status_ok()
+
+
+@pytest.mark.parametrize("T,H,E,K,I,clamp", [(64, 512, 8, 2, 256, 0.0), (300, 1024, 16, 4, 768, 0.0),
+                                             (5, 256, 4, 1, 16, 0.0), (128, 2048, 32, 8, 176, 1.5)])
+def test_grouped_gemm_swiglu_epilogue(T, H, E, K, I, clamp):
+    """Gate / up rows interleaved in blocks of [16 gate | 16 up]: the grouped GEMM applies SwiGLU
+    (clamped or not) in its epilogue. Compared with the fp32 definition of GEMM -> round -> SwiGLU
+    and with the unfused pair of kernels; I = 16 and 176 leave partial 128-row weight tiles."""
+    g = torch.Generator(device=DEV).manual_seed(2)
+    x = (torch.randn(T, H, device=DEV, generator=g) * 0.5).bfloat16()
+    w13 = (torch.randn(E, 2 * I, H, device=DEV, generator=g) * 0.08).bfloat16()
+    w2 = (torch.randn(E, H, I, device=DEV, generator=g) * 0.05).bfloat16()
+    wts, ids = moe_ops.softmax_topk(torch.randn(T, E, device=DEV, generator=g), K, True)
+    w_il = moe_ops.interleave16(w13)
+    assert torch.equal(moe_ops.deinterleave16(w_il), w13)
+    fused = moe_ops.experts_forward(x, wts, ids, w_il, w2, 0, clamp, il16=True)
+    plain = moe_ops.experts_forward(x, wts, ids, w13, w2, 0, clamp)
+    want = ref.moe_ffn(x.cpu(), wts.cpu(), ids.cpu(), w13.cpu(), w2.cpu(), 0, clamp)
+    close(fused, want, atol=2e-2, rtol=3e-2, what="experts_forward with the SwiGLU epilogue")
+    close(fused, plain, atol=1e-2, rtol=2e-2, what="SwiGLU epilogue vs the unfused pair")
+    status_ok()
