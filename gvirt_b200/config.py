@@ -283,6 +283,10 @@ class EnvFlags:
     disable_symm: bool = False           # GVIRT_DISABLE_SYMM: use NCCL instead of own collectives
     enable_graph: bool = True            # GVIRT_ENABLE_GRAPH: CUDA-graph decode buckets
     moe_alltoall: bool = True            # GVIRT_MOE_ALLTOALL: fused dispatch/combine vs AG/RS
+    moe_a2a_tp_slices: bool = False      # GVIRT_MOE_A2A_TP_SLICES: with tensor-parallel attention, run the
+                                         # dispatch/combine exchange on 1/tp token slices instead of
+                                         # local experts + all-reduce (measured slower at EP2: the
+                                         # replicated tokens need no dispatch, and K rows travel per token)
     active_tokens_ratio_per_ep: float = 1.0  # GVIRT_ACTIVE_TOKENS_RATIO_PER_EP: receive-region
     #                                      size as a fraction of the worst case tokens * top_k
     deterministic: bool = True           # GVIRT_DETERMINISTIC: fixed-order reductions
@@ -326,6 +330,7 @@ class EnvFlags:
         f.disable_symm = parse_bool(e.get("GVIRT_DISABLE_SYMM"), f.disable_symm)
         f.enable_graph = parse_bool(e.get("GVIRT_ENABLE_GRAPH"), f.enable_graph)
         f.moe_alltoall = parse_bool(e.get("GVIRT_MOE_ALLTOALL"), f.moe_alltoall)
+        f.moe_a2a_tp_slices = parse_bool(e.get("GVIRT_MOE_A2A_TP_SLICES"), f.moe_a2a_tp_slices)
         f.active_tokens_ratio_per_ep = float(e.get("GVIRT_ACTIVE_TOKENS_RATIO_PER_EP",
                                                    f.active_tokens_ratio_per_ep))
         f.deterministic = parse_bool(e.get("GVIRT_DETERMINISTIC"), f.deterministic)

@@ -8,23 +8,28 @@
 //
 // The reference runs these as separate launches in its "comm optimize" layer loop —
 // XliteOpReduceScatter after the matmul, XliteOpAllGather before the next one
-// (xlite/csrc/model.cpp:1343-1406, 583-594, 836-850). Here both are one tcgen05 GEMM kernel each:
+// (xlite/csrc/model.cpp:1343-1406, 583-594, 836-850). Here both are one persistent tcgen05 GEMM
+// kernel each, built like the prefill GEMM (gemm_persist.cu): one CTA per SM walks a list of
+// 128-token x 256-feature tiles, the fp32 accumulator is double-buffered in TMEM so the epilogue
+// of one tile (which is where the communication happens) overlaps the K loop of the next.
 //
-//   gemm_rs: every rank computes all 128-token x 128-feature tiles, visiting the token blocks in the
-//   rotated order rank+1, rank+2, ..., rank, so tiles owned by other ranks are produced first: their
-//   epilogue writes the bf16 partial straight into the owner's receive region over NVLink and raises
-//   the owner's (tile, source) flag with a system-scope release. The rank's own tiles come last; their
-//   epilogue waits (bounded) until the R-1 remote partials have arrived, adds them in rank order to
-//   the accumulator it still holds in TMEM and writes the reduced rows. Transfers overlap the
-//   remaining tiles' math.
+//   gemm_rs: every rank computes all tiles, visiting the token blocks in the rotated order
+//   rank+1, rank+2, ..., rank, so tiles owned by other ranks are produced first. Their epilogue
+//   rounds the partial to bf16, transposes it through shared memory and writes whole 128-byte row
+//   segments into the owner's receive region over NVLink (a thread-per-row store pattern would put
+//   16-byte packets on the links and is packet-rate bound at a fraction of the bandwidth), then
+//   raises the owner's (tile, source) flag with a system-scope release. The rank's own tiles come
+//   last; their epilogue waits (bounded) until the R-1 remote partials have arrived, adds them in
+//   rank order to its own rounded partial and writes the reduced rows, again in row segments with
+//   every remote load of a step in flight before the first is consumed.
 //
 //   ag_gemm: a staging launch PUSHES the local token slice into every rank's staging region
 //   `[parity][source rank][rows][K]` (so each slice crosses NVLink exactly once per destination)
 //   and publishes a flag; the GEMM's TMA producer then loads every token tile from this GPU's own
 //   memory (plain, non-multicast TMA through tensor maps that live in global memory, one per source
-//   rank and parity), own tiles first, waiting (bounded) on the source's flag before the first load
-//   of its rows. Loading the tiles straight from the peers instead would re-read a remote tile once
-//   per output-column tile.
+//   rank and parity), own token block first, waiting (bounded) on a source's flag before the first
+//   load of its rows. Loading the tiles straight from the peers instead would re-read a remote tile
+//   once per output-column tile.
 //
 // Generation counters live on the device (CUDA-graph replay safe); staging / receive regions are
 // double-buffered by the generation's parity (see parallel/symm.py for why two suffice).
@@ -37,9 +42,15 @@ namespace gemm {
 int cached_tmap_bf16(CUtensorMap* out, const void* base, long long rows, long long cols,
                      long long row_stride_elems, int box_rows);
 
-constexpr int SP_BN = 128;
+constexpr int SP_BN = 256;           // features per tile (TMEM columns of one accumulator buffer)
 constexpr int SP_MAX_RANKS = 16;
 constexpr int SP_RS_MAX_RANKS = 8;   // ranks the reduce phase of gemm_rs unrolls over
+constexpr int SP_GROUP = 16;         // token tiles that share a sweep over the feature tiles (L2 reuse)
+constexpr int SP_CHUNK = 64;         // features transposed through shared memory at a time
+constexpr int SP_PITCH = SP_CHUNK * 2 + 16;            // bytes per staged row (+16: bank spread)
+constexpr int SP_STAGING = 4 * 32 * SP_PITCH;          // four epilogue warps x 32 rows
+using SpCfg = Cfg<SP_BN, 200>;
+constexpr int SP_SMEM_BYTES = SpCfg::SMEM_BYTES + SP_STAGING;
 
 __device__ __forceinline__ void sp_epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 __device__ __forceinline__ uint4 sp_ld_sys16(const void* p) {
@@ -60,109 +71,289 @@ struct SpArgs {
   int rank, R, m_r_cap;
 };
 
-// ------------------------------------------------------------------ GEMM -> reduce-scatter
+struct SpTile {
+  int tm, tn;
+};
+// tile t of the walk -> (token tile, feature tile): groups of SP_GROUP token tiles sweep the feature
+// tiles together; `shift` rotates the token tiles so that a chosen rank's block comes first / last
+__device__ __forceinline__ SpTile sp_locate(int t, int tilesM, int tilesN, int shift) {
+  const int per_group = SP_GROUP * tilesN;
+  const int g = t / per_group;
+  const int first = g * SP_GROUP;
+  const int gsz = (tilesM - first) < SP_GROUP ? (tilesM - first) : SP_GROUP;
+  const int r = t - g * per_group;
+  SpTile tl;
+  tl.tm = (first + r % gsz + shift) % tilesM;
+  tl.tn = r / gsz;
+  return tl;
+}
+
+// MODE 1: GEMM -> reduce-scatter (x is this rank's [M, K_r]); MODE 2: all-gather -> GEMM (token tiles
+// come from the staging region through `maps`).
+template <int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_rs_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
-               bf16* __restrict__ out, int M, int N, int K, long long ldo, int tilesM, int tilesN,
+sp_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const CUtensorMap* __restrict__ maps,
+               const __grid_constant__ CUtensorMap tmW, bf16* __restrict__ out,
+               const bf16* __restrict__ bias, int M, int N, int K, long long ldo, int tilesM, int tilesN,
                SpArgs a, unsigned int* status) {
-  using C = Cfg<SP_BN, 220>;
+  using C = SpCfg;
+  constexpr int BN = SP_BN;
+  constexpr int TCOLS = 2 * BN;
+  static_assert(TCOLS == 512, "the two accumulator buffers take the whole TMEM");
   extern __shared__ uint8_t smem_raw[];
-  const Shared sh = carve<C>(smem_raw);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const unsigned int gen = *reinterpret_cast<volatile unsigned int*>(&a.state[0]) + 1u;
-  const int tiles_per_rank = tilesM / a.R;
-  const int tn = blockIdx.x % tilesN;
-  const int tm_seq = blockIdx.x / tilesN;
-  const int tm = (tm_seq + (a.rank + 1) * tiles_per_rank) % tilesM;  // other ranks' blocks first
-  const int owner = tm / tiles_per_rank;
-  const int row_local0 = (tm % tiles_per_rank) * BM;
-  const int tile_id = (tm % tiles_per_rank) * tilesN + tn;
+  // gemm_rs opens a new generation; ag_gemm runs in the one its staging launch opened
+  const unsigned int gen = *reinterpret_cast<volatile unsigned int*>(&a.state[0]) + (MODE == 1 ? 1u : 0u);
+  const int total = tilesM * tilesN;
   const int nkb = (K + BK - 1) / BK;
+  const int tpr = tilesM / a.R;                       // token tiles per rank
+  const int shift = (MODE == 1 ? (a.rank + 1) : a.rank) * tpr;   // RS: own block last; AG: own block first
 
-  const uint32_t tmem_base = run_mainloop<C>(sh, &tmX, &tmW, tm * BM, tn * SP_BN, 0, nkb, status);
+  uintptr_t base = (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023);
+  uint8_t* ring = reinterpret_cast<uint8_t*>(base);
+  uint64_t* full = reinterpret_cast<uint64_t*>(ring + C::STAGES * C::STAGE_BYTES);
+  uint64_t* empty = full + C::STAGES;
+  uint64_t* tfull = empty + C::STAGES;   // [2] accumulator buffer complete
+  uint64_t* tempty = tfull + 2;          // [2] accumulator buffer drained
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  uint8_t* staging = ring + C::STAGES * C::STAGE_BYTES + 256;
+  static_assert((2 * C::STAGES + 4) * 8 + 4 <= 256, "barriers must fit behind the ring");
 
-  if (warp >= 2) {
+  if (warp == 0 && sm100::elect_one()) {
+    if (MODE == 1) sm100::tma_prefetch_desc(&tmX);
+    sm100::tma_prefetch_desc(&tmW);
+    for (int s = 0; s < C::STAGES; ++s) {
+      sm100::mbar_init(&full[s], 1);
+      sm100::mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      sm100::mbar_init(&tfull[b], 1);
+      sm100::mbar_init(&tempty[b], 4);  // one arrival per epilogue warp
+    }
+    sm100::mbar_fence_init();
+  }
+  if (warp == 1) {
+    sm100::tmem_alloc(tmem_slot, TCOLS);
+    sm100::tmem_relinquish();
+  }
+  sm100::tc_fence_before();
+  __syncthreads();
+  sm100::tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+  if (warp == 0) {
+    if (sm100::elect_one()) {
+      uint32_t gk = 0, seen = 1u << a.rank;     // AG: sources whose staged rows are known to be complete
+      bool ok = true;
+      for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+        const SpTile tl = sp_locate(t, tilesM, tilesN, shift);
+        const CUtensorMap* tx = &tmX;
+        int row0 = tl.tm * BM;
+        if (MODE == 2) {
+          const int owner = tl.tm / tpr;
+          if (!((seen >> owner) & 1u)) {
+            // the TMA loads must not touch a source's rows before that source has published them
+            const unsigned int* f =
+                reinterpret_cast<const unsigned int*>(static_cast<char*>(a.peers[a.rank]) + a.flags_off) + owner;
+            if (!wait_ge_sys(f, gen, peer_budget(status))) atomicOr(status, GV_ST_TIMEOUT_PEER);
+            // the flag was observed through the generic proxy; the tile loads go through the async proxy
+            asm volatile("fence.proxy.async;" ::: "memory");
+            seen |= 1u << owner;
+          }
+          tx = maps + (gen & 1u) * a.R + owner;
+          row0 = (tl.tm % tpr) * BM;
+        }
+        for (int i = 0; i < nkb; ++i, ++gk) {
+          const int s = gk % C::STAGES;
+          if (!sm100::mbar_wait(&empty[s], ((gk / C::STAGES) & 1u) ^ 1u)) {
+            atomicOr(status, GV_ST_TIMEOUT_TMA);
+            ok = false;
+            break;
+          }
+          uint8_t* sp = ring + s * C::STAGE_BYTES;
+          sm100::mbar_expect_tx(&full[s], C::STAGE_BYTES);
+          sm100::tma_load_2d(sp, tx, &full[s], i * BK, row0);
+          sm100::tma_load_2d(sp + C::P_BYTES, &tmW, &full[s], i * BK, tl.tn * BN);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (sm100::elect_one()) {
+      constexpr uint32_t idesc = sm100::make_idesc(BM, BN, 1, 1);
+      uint32_t gk = 0, it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
+        const uint32_t buf = it & 1u;
+        if (!sm100::mbar_wait(&tempty[buf], ((it >> 1) & 1u) ^ 1u)) {
+          atomicOr(status, GV_ST_TIMEOUT_MMA);
+          break;
+        }
+        sm100::tc_fence_after();
+        for (int i = 0; i < nkb; ++i, ++gk) {
+          const int s = gk % C::STAGES;
+          if (!sm100::mbar_wait(&full[s], (gk / C::STAGES) & 1u)) {
+            atomicOr(status, GV_ST_TIMEOUT_MMA);
+            ok = false;
+            break;
+          }
+          sm100::tc_fence_after();
+          const uint32_t pa = sm100::smem_u32(ring + s * C::STAGE_BYTES);
+          const uint64_t da = sm100::smem_desc_sw128(pa);
+          const uint64_t db = sm100::smem_desc_sw128(pa + C::P_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            sm100::mma_f16_ss(tmem_base + buf * BN, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k),
+                              idesc, (uint32_t)((i | k) != 0));
+          sm100::tc_commit(&empty[s]);
+        }
+        if (ok) sm100::tc_commit(&tfull[buf]);
+      }
+    }
+  } else {
     const int quad = warp & 3;
-    const int row = row_local0 + quad * 32 + lane;  // row inside the owner's slice
-    const int n0 = tn * SP_BN;
+    uint8_t* stg = staging + quad * 32 * SP_PITCH;      // this warp's 32 rows of the chunk
+    const int srow = lane >> 3, piece = lane & 7;       // write-out: 8 lanes cover one 128-byte row segment
     const long long par_elems = a.data_stride / 2;
-    wait_accum(sh, status);
-    if (owner != a.rank) {
-      bf16* dst = reinterpret_cast<bf16*>(static_cast<char*>(a.peers[owner]) + a.data_off) +
-                  (long long)(gen & 1u) * par_elems + ((long long)a.rank * a.m_r_cap + row) * N + n0;
+    uint32_t it = 0;
+    for (int t = blockIdx.x; t < total; t += gridDim.x, ++it) {
+      const SpTile tl = sp_locate(t, tilesM, tilesN, shift);
+      const uint32_t buf = it & 1u;
+      const bool ok = sm100::mbar_wait(&tfull[buf], (it >> 1) & 1u);
+      __syncwarp();
+      if (!ok) {
+        if (lane == 0) atomicOr(status, GV_ST_TIMEOUT_EPI);
+        break;
+      }
+      sm100::tc_fence_after();
+      const int n0 = tl.tn * BN;
+      if (MODE == 2) {
+        const int p = tl.tm * BM + quad * 32 + lane;  // token row of this thread
+        bf16* orow = out + (long long)p * ldo;
 #pragma unroll 1
-      for (int c = 0; c < SP_BN; c += 16) {
-        uint32_t r[16];
-        sm100::tmem_ld16(tmem_addr(tmem_base, quad, c), r);
-        sm100::tmem_ld_wait();
-        if (n0 + c + 16 <= N) {
+        for (int c = 0; c < BN; c += 16) {
+          uint32_t r[16];
+          sm100::tmem_ld16(tmem_addr(tmem_base, quad, (int)(buf * BN) + c), r);
+          sm100::tmem_ld_wait();
+          const int q = n0 + c;
+          if (p < M && q < N) {
+            if (q + 16 <= N) {
+              float f[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                f[j] = __uint_as_float(r[j]);
+                if (bias != nullptr) f[j] += bf2f(bias[q + j]);
+              }
+              st8(orow + q, pack8(f));
+              st8(orow + q + 8, pack8(f + 8));
+            } else {
+              for (int j = 0; j < 16 && q + j < N; ++j) {
+                float v = __uint_as_float(r[j]);
+                if (bias != nullptr) v += bf2f(bias[q + j]);
+                orow[q + j] = f2bf(v);
+              }
+            }
+          }
+        }
+        sm100::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) sm100::mbar_arrive(&tempty[buf]);
+        continue;
+      }
+      // ---- MODE 1: reduce-scatter epilogue
+      const int owner = tl.tm / tpr;
+      const int row_local0 = (tl.tm % tpr) * BM + quad * 32;        // first row of this warp in the owner's slice
+      const int tile_id = (tl.tm % tpr) * tilesN + tl.tn;
+      const bool mine = owner == a.rank;
+      if (mine) {
+        const int s = (int)threadIdx.x - 64;
+        if (s < a.R && s != a.rank) {
+          const unsigned int* f = reinterpret_cast<const unsigned int*>(static_cast<char*>(a.peers[a.rank]) +
+                                                                        a.flags_off) +
+                                  (size_t)tile_id * SP_MAX_RANKS + s;
+          if (!wait_ge_sys(f, gen, peer_budget(status))) atomicOr(status, GV_ST_TIMEOUT_PEER);
+        }
+        sp_epi_bar();
+      }
+      bf16* push = reinterpret_cast<bf16*>(static_cast<char*>(a.peers[owner]) + a.data_off) +
+                   (long long)(gen & 1u) * par_elems + ((long long)a.rank * a.m_r_cap + row_local0) * N + n0;
+      const bf16* recv = reinterpret_cast<const bf16*>(static_cast<char*>(a.peers[a.rank]) + a.data_off) +
+                         (long long)(gen & 1u) * par_elems + (long long)row_local0 * N + n0;
+      bf16* orow0 = out + (long long)row_local0 * ldo + n0;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += SP_CHUNK) {
+        // accumulator chunk -> bf16 -> this warp's staging rows (lane = row)
+#pragma unroll
+        for (int c = 0; c < SP_CHUNK; c += 16) {
+          uint32_t r[16];
+          sm100::tmem_ld16(tmem_addr(tmem_base, quad, (int)(buf * BN) + c0 + c), r);
+          sm100::tmem_ld_wait();
           float f[16];
 #pragma unroll
           for (int j = 0; j < 16; ++j) f[j] = __uint_as_float(r[j]);
-          st8(dst + c, pack8(f));
-          st8(dst + c + 8, pack8(f + 8));
+          *reinterpret_cast<bf16x8*>(stg + lane * SP_PITCH + c * 2) = pack8(f);
+          *reinterpret_cast<bf16x8*>(stg + lane * SP_PITCH + c * 2 + 16) = pack8(f + 8);
         }
-      }
-      sp_epi_bar();
-      if (threadIdx.x == 64) {
-        __threadfence_system();
-        st_release_sys(reinterpret_cast<unsigned int*>(static_cast<char*>(a.peers[owner]) + a.flags_off) +
-                           (size_t)tile_id * SP_MAX_RANKS + a.rank,
-                       gen);
-      }
-    } else {
-      const int s = (int)threadIdx.x - 64;
-      if (s < a.R && s != a.rank) {
-        const unsigned int* f = reinterpret_cast<const unsigned int*>(static_cast<char*>(a.peers[a.rank]) +
-                                                                      a.flags_off) +
-                                (size_t)tile_id * SP_MAX_RANKS + s;
-        if (!wait_ge_sys(f, gen, peer_budget(status))) atomicOr(status, GV_ST_TIMEOUT_PEER);
-      }
-      sp_epi_bar();
-      const bf16* base = reinterpret_cast<const bf16*>(static_cast<char*>(a.peers[a.rank]) + a.data_off) +
-                         (long long)(gen & 1u) * par_elems;
-      bf16* orow = out + (long long)row * ldo + n0;
-#pragma unroll 1
-      for (int c = 0; c < SP_BN; c += 16) {
-        uint32_t r[16];
-        sm100::tmem_ld16(tmem_addr(tmem_base, quad, c), r);
-        sm100::tmem_ld_wait();
-        if (n0 + c + 16 > N) continue;
-        // all remote partials of this chunk are requested before any is consumed: up to
-        // 2 (R - 1) independent 16-byte loads in flight per thread instead of a chain of them
-        uint4 v[SP_RS_MAX_RANKS][2];
+        if (c0 + SP_CHUNK >= BN) {
+          // last read of this accumulator buffer: hand it back to the MMA warp
+          sm100::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) sm100::mbar_arrive(&tempty[buf]);
+        }
+        __syncwarp();
+        const int col = n0 + c0 + piece * 8;            // first of this lane's 8 features
+        if (!mine) {
 #pragma unroll
-        for (int s = 0; s < SP_RS_MAX_RANKS; ++s) {
-          if (s < a.R && s != a.rank) {
-            const bf16* src = base + ((long long)s * a.m_r_cap + row) * N + n0 + c;
-            v[s][0] = sp_ld_sys16(src);
-            v[s][1] = sp_ld_sys16(src + 8);
+          for (int rr = 0; rr < 32; rr += 4) {
+            const int row = rr + srow;
+            const uint4 v = *reinterpret_cast<const uint4*>(stg + row * SP_PITCH + piece * 16);
+            if (col + 8 <= N) *reinterpret_cast<uint4*>(push + (long long)row * N + c0 + piece * 8) = v;
+          }
+        } else {
+#pragma unroll 2
+          for (int rr = 0; rr < 32; rr += 4) {
+            const int row = rr + srow;
+            if (col + 8 > N) continue;
+            // every remote partial of this row segment is requested before any is consumed
+            uint4 v[SP_RS_MAX_RANKS];
+#pragma unroll
+            for (int s = 0; s < SP_RS_MAX_RANKS; ++s)
+              if (s < a.R && s != a.rank)
+                v[s] = sp_ld_sys16(recv + ((long long)s * a.m_r_cap + row) * N + c0 + piece * 8);
+            const uint4 own = *reinterpret_cast<const uint4*>(stg + row * SP_PITCH + piece * 16);
+            float acc[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll
+            for (int s = 0; s < SP_RS_MAX_RANKS; ++s) {  // rank order, so every rank rounds alike
+              if (s >= a.R) continue;
+              float f[8];
+              unpack8(*reinterpret_cast<const bf16x8*>(s == a.rank ? &own : &v[s]), f);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) acc[j] += f[j];
+            }
+            st8(orow0 + (long long)row * ldo + c0 + piece * 8, pack8(acc));
           }
         }
-        float acc[16];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) acc[j] = 0.f;
-#pragma unroll
-        for (int s = 0; s < SP_RS_MAX_RANKS; ++s) {  // rank order; this rank's own partial is the accumulator
-          if (s >= a.R) continue;
-          if (s == a.rank) {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) acc[j] += bf2f(f2bf(__uint_as_float(r[j])));
-          } else {
-            float f[16];
-            unpack8(*reinterpret_cast<const bf16x8*>(&v[s][0]), f);
-            unpack8(*reinterpret_cast<const bf16x8*>(&v[s][1]), f + 8);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) acc[j] += f[j];
-          }
+        __syncwarp();                                    // the staging rows are rewritten by the next chunk
+      }
+      if (!mine) {
+        sp_epi_bar();                                    // all four warps' rows are on their way
+        if (threadIdx.x == 64) {
+          __threadfence_system();
+          st_release_sys(reinterpret_cast<unsigned int*>(static_cast<char*>(a.peers[owner]) + a.flags_off) +
+                             (size_t)tile_id * SP_MAX_RANKS + a.rank,
+                         gen);
         }
-        st8(orow + c, pack8(acc));
-        st8(orow + c + 8, pack8(acc + 8));
       }
     }
   }
-  finish<C>(sh, tmem_base);
-  if (threadIdx.x == 0) {
+  sm100::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    sm100::tc_fence_after();
+    sm100::tmem_dealloc(tmem_base, TCOLS);
+  }
+  if (MODE == 1 && threadIdx.x == 0) {
     __threadfence();
     if (atomicAdd(&a.state[1], 1u) == gridDim.x - 1) {
       a.state[1] = 0;
@@ -208,71 +399,6 @@ __global__ void ag_stage_kernel(const bf16* __restrict__ x, long long n_elems, l
   }
 }
 
-// maps: global array [2 * R] of tensor maps over the source slots of this rank's staging region
-// (parity-major).
-__global__ void __launch_bounds__(NUM_THREADS, 1)
-ag_gemm_kernel(const CUtensorMap* __restrict__ maps, const __grid_constant__ CUtensorMap tmW,
-               bf16* __restrict__ out, const bf16* __restrict__ bias, int M, int N, int K, long long ldo,
-               int tilesM, int tilesN, SpArgs a, unsigned int* status) {
-  using C = Cfg<SP_BN, 220>;
-  extern __shared__ uint8_t smem_raw[];
-  const Shared sh = carve<C>(smem_raw);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const unsigned int gen = *reinterpret_cast<volatile unsigned int*>(&a.state[0]);  // staged already
-  const int tiles_per_rank = tilesM / a.R;
-  const int tn = blockIdx.x % tilesN;
-  const int tm_seq = blockIdx.x / tilesN;
-  const int tm = (tm_seq + a.rank * tiles_per_rank) % tilesM;  // own token block first
-  const int owner = tm / tiles_per_rank;
-  const int row_local0 = (tm % tiles_per_rank) * BM;
-  const int nkb = (K + BK - 1) / BK;
-  const CUtensorMap* tmX = maps + (gen & 1u) * a.R + owner;
-  // the TMA producer must not touch a peer's staging buffer before that peer has published it
-  if (warp == 0 && owner != a.rank) {
-    if (lane == 0) {
-      const unsigned int* f =
-          reinterpret_cast<const unsigned int*>(static_cast<char*>(a.peers[a.rank]) + a.flags_off) + owner;
-      if (!wait_ge_sys(f, gen, peer_budget(status))) atomicOr(status, GV_ST_TIMEOUT_PEER);
-    }
-    __syncwarp();
-    // the flag was observed through the generic proxy; the tile loads go through the async proxy
-    asm volatile("fence.proxy.async;" ::: "memory");
-  }
-  const uint32_t tmem_base = run_mainloop<C>(sh, tmX, &tmW, row_local0, tn * SP_BN, 0, nkb, status);
-  if (warp >= 2) {
-    const int quad = warp & 3;
-    const int row = tm * BM + quad * 32 + lane;
-    const int n0 = tn * SP_BN;
-    wait_accum(sh, status);
-    bf16* orow = out + (long long)row * ldo + n0;
-#pragma unroll 1
-    for (int c = 0; c < SP_BN; c += 16) {
-      uint32_t r[16];
-      sm100::tmem_ld16(tmem_addr(tmem_base, quad, c), r);
-      sm100::tmem_ld_wait();
-      if (row < M) {
-        if (n0 + c + 16 <= N) {
-          float f[16];
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            f[j] = __uint_as_float(r[j]);
-            if (bias != nullptr) f[j] += bf2f(bias[n0 + c + j]);
-          }
-          st8(orow + c, pack8(f));
-          st8(orow + c + 8, pack8(f + 8));
-        } else {
-          for (int j = 0; j < 16 && n0 + c + j < N; ++j) {
-            float v = __uint_as_float(r[j]);
-            if (bias != nullptr) v += bf2f(bias[n0 + c + j]);
-            orow[c + j] = f2bf(v);
-          }
-        }
-      }
-    }
-  }
-  finish<C>(sh, tmem_base);
-}
-
 static bool g_rs_conf = false, g_ag_conf = false;
 
 }  // namespace gemm
@@ -295,19 +421,19 @@ static SpArgs sp_args(const void* peers, long long data_off, long long data_stri
   return a;
 }
 
-// x [M, K_r], w [N, K_r] (this rank's K shard), out [M / R, N]. M % (128 * R) == 0, N % 16 == 0.
-// Receive region: 2 * R * m_r_cap * N bf16; flags: (m_r_cap / 128) * ceil(N / 128) * 16 words.
+// x [M, K_r], w [N, K_r] (this rank's K shard), out [M / R, N]. M % (128 * R) == 0, N % 8 == 0.
+// Receive region: 2 * R * m_r_cap * N bf16; flags: (m_r_cap / 128) * ceil(N / 256) * 16 words.
 extern "C" int gv_gemm_rs(const void* x, const void* w, void* out, long long M, long long N, long long K,
                           long long ldx, long long ldw, long long ldo, const void* peers,
                           long long recv_off, long long recv_stride, long long cnt_off, void* state,
                           long long rank, long long R, long long m_r_cap, void* stream) {
   if (!x || !w || !out || !peers || !state) return GV_EINVAL;
-  if (M <= 0 || M % (BM * R) || (N & 15) || (K & 7) || (ldx & 7) || (ldw & 7) || (ldo & 7)) return GV_EINVAL;
+  if (M <= 0 || M % (BM * R) || (N & 7) || (K & 7) || (ldx & 7) || (ldw & 7) || (ldo & 7)) return GV_EINVAL;
   if (M / R > m_r_cap || R > SP_RS_MAX_RANKS) return GV_ETOOBIG;
   if ((long long)R * m_r_cap * N * 2 > recv_stride) return GV_ETOOBIG;
-  using C = Cfg<SP_BN, 220>;
+  auto kern = sp_gemm_kernel<1>;
   if (!g_rs_conf) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_rs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SP_SMEM_BYTES);
     if (e != cudaSuccess) {
       set_last_error("gemm_rs: smem attr", e);
       return GV_ECUDA;
@@ -319,9 +445,12 @@ extern "C" int gv_gemm_rs(const void* x, const void* w, void* out, long long M, 
   if ((rc = cached_tmap_bf16(&tmX, x, M, K, ldx, BM)) != GV_OK) return rc;
   if ((rc = cached_tmap_bf16(&tmW, w, N, K, ldw, SP_BN)) != GV_OK) return rc;
   const int tilesM = (int)(M / BM), tilesN = ceil_div(N, SP_BN);
+  long long grid = (long long)tilesM * tilesN;
+  if (grid > num_sms()) grid = num_sms();
   SpArgs a = sp_args(peers, recv_off, recv_stride, cnt_off, state, rank, R, m_r_cap);
-  gemm_rs_kernel<<<(unsigned)(tilesM * tilesN), NUM_THREADS, C::SMEM_BYTES, (cudaStream_t)stream>>>(
-      tmX, tmW, (bf16*)out, (int)M, (int)N, (int)K, ldo, tilesM, tilesN, a, status_word());
+  kern<<<(unsigned)grid, NUM_THREADS, SP_SMEM_BYTES, (cudaStream_t)stream>>>(
+      tmX, (const CUtensorMap*)nullptr, tmW, (bf16*)out, (const bf16*)nullptr, (int)M, (int)N, (int)K, ldo,
+      tilesM, tilesN, a, status_word());
   return check_launch("gv_gemm_rs");
 }
 
@@ -361,9 +490,9 @@ extern "C" int gv_ag_gemm(const void* x_local, const void* w, const void* bias, 
   if (!x_local || !w || !out || !maps_dev || !peers || !state) return GV_EINVAL;
   if (M <= 0 || M % (BM * R) || (K & 7) || (ldw & 7) || (ldo & 7)) return GV_EINVAL;
   if (M / R > m_r_cap || R * m_r_cap * K * 2 > stage_stride) return GV_ETOOBIG;
-  using C = Cfg<SP_BN, 220>;
+  auto kern = sp_gemm_kernel<2>;
   if (!g_ag_conf) {
-    cudaError_t e = cudaFuncSetAttribute(ag_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SP_SMEM_BYTES);
     if (e != cudaSuccess) {
       set_last_error("ag_gemm: smem attr", e);
       return GV_ECUDA;
@@ -381,8 +510,10 @@ extern "C" int gv_ag_gemm(const void* x_local, const void* w, const void* bias, 
   int rc;
   if ((rc = cached_tmap_bf16(&tmW, w, N, K, ldw, SP_BN)) != GV_OK) return rc;
   const int tilesM = (int)(M / BM), tilesN = ceil_div(N, SP_BN);
-  ag_gemm_kernel<<<(unsigned)(tilesM * tilesN), NUM_THREADS, C::SMEM_BYTES, st>>>(
-      (const CUtensorMap*)maps_dev, tmW, (bf16*)out, (const bf16*)bias, (int)M, (int)N, (int)K, ldo, tilesM,
+  long long grid = (long long)tilesM * tilesN;
+  if (grid > num_sms()) grid = num_sms();
+  kern<<<(unsigned)grid, NUM_THREADS, SP_SMEM_BYTES, st>>>(
+      tmW, (const CUtensorMap*)maps_dev, tmW, (bf16*)out, (const bf16*)bias, (int)M, (int)N, (int)K, ldo, tilesM,
       tilesN, a, status_word());
   return check_launch("gv_ag_gemm");
 }

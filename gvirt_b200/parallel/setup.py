@@ -19,10 +19,18 @@ def heap_bytes(cfg: ModelConfig, world: int) -> int:
     push = 6 * (2 * 16 * world * (1 << 17))
     sp = 0
     if cfg.max_num_batched_tokens >= flags().comm_optimize_len and world <= flags().sp_max_ranks:
-        # GEMM -> reduce-scatter receive regions (2 projections x 2 parities x R x 2048 rows x H)
-        # and all-gather -> GEMM staging (2 inputs x 2 parities x R x 2048 rows x H), bf16
-        sp = 2 * 2 * world * 2048 * H * 2 + 2 * 2 * world * 2048 * H * 2
+        # GEMM -> reduce-scatter receive region and all-gather -> GEMM staging, each 2 parities x R
+        # sources x rows-per-rank x H bf16 (the two projections of a kind share a region); the
+        # widest activation that is gathered or scattered has H columns
+        cap = sp_rows_per_rank(cfg, world)
+        sp = 2 * (2 * world * cap * H * 2) + (8 << 20)
     return max(1 << 30, gemm_ar + push + sp + (64 << 20))
+
+
+def sp_rows_per_rank(cfg: ModelConfig, world: int) -> int:
+    """Token rows per rank that the sequence-parallel regions hold: one full step, padded to the
+    128 * world rows the fused kernels work in."""
+    return max(128, -(-cfg.max_num_batched_tokens // (128 * world)) * 128)
 
 
 def a2a_bytes(cfg: ModelConfig, world: int, tokens_cap: int) -> int:
@@ -62,10 +70,10 @@ def attach_device_comm(ctx, cfg: ModelConfig) -> None:
     if ctx.device.type != "cuda" or ctx.world == 1:
         return
     ep_bytes = 0
-    # the fused exchange serves data-parallel attention (every rank dispatches its own tokens) and
-    # tensor-parallel attention over the same ranks as the experts (every rank dispatches a 1/tp
-    # slice of the replicated tokens)
-    sliced = ctx.dp == 1 and ctx.tp > 1 and ctx.ep == ctx.tp
+    # the fused exchange serves data-parallel attention (every rank dispatches its own tokens) and,
+    # on request (GVIRT_MOE_A2A_TP_SLICES), tensor-parallel attention over the same ranks as the
+    # experts (every rank dispatches a 1/tp slice of the replicated tokens)
+    sliced = ctx.dp == 1 and ctx.tp > 1 and ctx.ep == ctx.tp and flags().moe_a2a_tp_slices
     use_a2a = cfg.is_moe and ctx.ep > 1 and flags().moe_alltoall and (ctx.dp > 1 or sliced)
     tokens_cap = cfg.max_num_batched_tokens
     if use_a2a:
@@ -73,5 +81,7 @@ def attach_device_comm(ctx, cfg: ModelConfig) -> None:
         tokens_cap = -(-cfg.max_num_batched_tokens // ctx.tp) if sliced else cfg.max_num_batched_tokens
         ep_bytes = a2a_bytes(cfg, ctx.ep, tokens_cap)
     attach_symmetric_heap(ctx, nbytes=heap_bytes(cfg, ctx.tp) if ctx.tp > 1 else 0, ep_nbytes=ep_bytes)
+    if getattr(ctx, "symm", None) is not None:
+        ctx.symm.sp_rows_cap = sp_rows_per_rank(cfg, ctx.tp)
     if use_a2a:
         attach_moe_a2a(ctx, cfg, tokens_cap=tokens_cap)

@@ -67,7 +67,11 @@ def main() -> int:
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     ctx = pstate.init_parallel(tp=world, dp=1, ep=1, timeout_s=120)
-    attach_symmetric_heap(ctx, nbytes=1 << 29)
+    # sequence-parallel regions: 2 kinds x 2 parities x prefill rows x widest column count, bf16
+    sp_rows = max(128, -(-args.prefill_tokens // (128 * ctx.tp)) * 128) if args.prefill_tokens > 0 else 0
+    attach_symmetric_heap(ctx, nbytes=(1 << 29) + 4 * ctx.tp * sp_rows * max(args.hidden, args.inter // ctx.tp) * 2)
+    if sp_rows and getattr(ctx, "symm", None) is not None:
+        ctx.symm.sp_rows_cap = sp_rows
     heap, dev, rank = ctx.symm, ctx.device, ctx.rank
     M, H = args.tokens, args.hidden
     for name, N, Kfull in (("o_proj", H, H), ("down_proj", H, args.inter)):

@@ -366,9 +366,46 @@ def case_prefill_attn(args):
                       "maxdiff": (o1.float() - o2.float()).abs().max().item()}), flush=True)
 
 
+def case_fused1(args):
+    """The kernels that fuse a GEMM with its collective, on a one-rank symmetric heap (the rank is
+    its own peer: staging, flags, generation counters and the reduce phase all run; nothing crosses
+    NVLink). Meant for single-GPU profiler captures of these kernels' compute side
+    (``--eager --chain 1 --reps 1``); multi-rank timings come from ``tools.comm_bench``."""
+    from types import SimpleNamespace
+    from ..config import ModelConfig
+    from ..ops import decode_ops as D
+    from ..ops import moe_ops
+    from ..parallel.moe_a2a import MoEA2A
+    from ..parallel.symm import SymmetricHeap
+    dev = torch.device("cuda", torch.cuda.current_device())
+    heap = SymmetricHeap(None, 0, 1, dev, nbytes=1 << 30)
+    out = {"case": "fused1"}
+    B, H, P = args.batch, 4096, args.tokens
+    x = (torch.randn(B, H, device=dev) * 0.1).bfloat16()
+    w = (torch.randn(H, H, device=dev) * 0.02).bfloat16()
+    res = torch.randn(B, H, device=dev).bfloat16()
+    ss = D.new_sumsq(H, dev)
+    out["gemm_allreduce_residual_sumsq_us"] = round(_time_us(
+        lambda i: heap.gemm_allreduce(x, w, out=res, residual=res, ss_out=ss), args), 2)
+    xp = (torch.randn(P, H, device=dev) * 0.1).bfloat16()
+    o1 = torch.empty(P, H, device=dev, dtype=torch.bfloat16)
+    out["gemm_rs_us"] = round(_time_us(lambda i: heap.gemm_reduce_scatter(xp, w, out=o1), args), 2)
+    out["ag_gemm_us"] = round(_time_us(lambda i: heap.allgather_gemm(xp, w, out=o1), args), 2)
+    E, K, inter, T = 32, 8, 768, 128
+    cfg = ModelConfig(hidden_size=2048, num_experts=E, num_experts_per_tok=K, moe_intermediate_size=inter)
+    a2a = MoEA2A(heap, cfg, SimpleNamespace(), tokens_cap=T, fp8=False)
+    L = SimpleNamespace(w13=moe_ops.interleave16((torch.randn(E, 2 * inter, 2048, device=dev) * 0.05).bfloat16()),
+                        w2=(torch.randn(E, 2048, inter, device=dev) * 0.05).bfloat16(), w13_il16=True)
+    xt = (torch.randn(T, 2048, device=dev) * 0.5).bfloat16()
+    wts, ids = moe_ops.softmax_topk(torch.randn(T, E, device=dev), K, True)
+    ot = torch.empty_like(xt)
+    out["moe_exchange_and_experts_us"] = round(_time_us(lambda i: a2a.forward(xt, wts, ids, L, ot), args), 2)
+    print(json.dumps(out), flush=True)
+
+
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("case", choices=["gemm", "swiglu", "attn", "mla", "layer", "prefill_gemm", "rope", "prefill_attn", "decode_gemm"])
+    ap.add_argument("case", choices=["gemm", "swiglu", "attn", "mla", "layer", "prefill_gemm", "rope", "prefill_attn", "decode_gemm", "fused1"])
     ap.add_argument("--tokens", type=int, default=8192)
     ap.add_argument("--with-persistent", action="store_true",
                     help="prefill_gemm: also time gemm_persist.cu (GVIRT_PREFILL_GEMM_PERSISTENT=2)")
@@ -393,7 +430,7 @@ def main() -> int:
     torch.manual_seed(0)
     {"gemm": case_gemm, "swiglu": lambda a: case_gemm(a, True), "attn": case_attn, "mla": case_mla,
      "layer": case_layer, "prefill_gemm": case_prefill_gemm, "rope": case_rope,
-     "prefill_attn": case_prefill_attn, "decode_gemm": case_decode_gemm}[args.case](args)
+     "prefill_attn": case_prefill_attn, "decode_gemm": case_decode_gemm, "fused1": case_fused1}[args.case](args)
     st = _native.read_status()
     if st:
         print(json.dumps({"status_word": st, "meaning": _native.describe_status(st)}))

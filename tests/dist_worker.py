@@ -258,7 +258,9 @@ def mode_gemm_sp_gpu(world):
     ctx = pstate.init_parallel(tp=world, dp=1, ep=1, timeout_s=90)
     attach_symmetric_heap(ctx, nbytes=1 << 30)
     heap, r, dev = ctx.symm, ctx.rank, ctx.device
-    for (M, N, Kfull) in [(128 * world, 256, 512), (1024 * world // 2, 4096, 4096), (256 * world, 1024, 2048)]:
+    # the last two: a feature count that leaves a partial 256-wide tile, and more tiles than SMs
+    for (M, N, Kfull) in [(128 * world, 256, 512), (1024 * world // 2, 4096, 4096), (256 * world, 1024, 2048),
+                          (256 * world, 336, 1024), (2048 * world, 4096, 2048)]:
         K = Kfull // world
         g = torch.Generator(device=dev).manual_seed(17)
         xf = (torch.randn(M, Kfull, device=dev, generator=g) * 0.5).bfloat16()
@@ -574,6 +576,8 @@ def mode_moe_tp_slice_gpu(world):
               max_num_batched_tokens=256, block_size=128, max_position_embeddings=512,
               num_experts=8 * world, num_experts_per_tok=4, moe_intermediate_size=512)
     cfg = tiny(tp_size=world, ep_size=world, **kw)
+    os.environ["GVIRT_MOE_A2A_TP_SLICES"] = "1"
+    gcfg.reload_flags()
     attach_device_comm(ctx, cfg)
     assert getattr(ctx, "moe_a2a", None) is not None, "the fused exchange was not attached"
     g = torch.Generator().manual_seed(3)
