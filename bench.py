@@ -55,7 +55,37 @@ def parse():
     ap.add_argument("--router-zipf", type=float, default=0.0,
                     help="MoE: bias the router so that expert popularity follows Zipf(alpha)")
     ap.add_argument("--max-tokens", type=int, default=8192, help="max_num_batched_tokens (prefill chunk)")
+    ap.add_argument("--kernel-table", default="",
+                    help="after the timed regions, replay the decode step 4 more times under torch.profiler and "
+                         "write rank 0's per-kernel device times to this file (diagnostic; never part of a number)")
     return ap.parse_args()
+
+
+def _kernel_table(graph, path, rank, barrier, reps=4):
+    """Per-kernel device time of the captured decode step on rank 0 (every rank replays)."""
+    from torch.profiler import ProfilerActivity, profile
+    barrier()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(reps):
+            graph.replay()
+        torch.cuda.synchronize()
+    barrier()
+    if rank != 0:
+        return
+    rows = []
+    for e in prof.key_averages():
+        t = getattr(e, "device_time_total", None)
+        if t is None:
+            t = getattr(e, "cuda_time_total", 0.0)
+        if t > 0:
+            rows.append((t / reps, e.count / reps, e.key))
+    rows.sort(reverse=True)
+    total = sum(r[0] for r in rows)
+    with open(path, "w") as f:
+        f.write(f"# device time per decode step by kernel, rank 0, mean of {reps} replays; sum {total:.1f} us\n")
+        f.write("# us_per_step  launches_per_step  us_per_launch  kernel\n")
+        for t, n, name in rows:
+            f.write(f"{t:10.1f} {n:8.1f} {t / max(n, 1e-9):9.2f}  {name[:150]}\n")
 
 
 class ClockSampler:
@@ -254,6 +284,8 @@ def main():
         launches = _native.LAUNCHES - l1
     clocks = sampler.stop() if rank == 0 else {}
     status = runner.check_status()
+    if args.kernel_table and key is not None and not args.no_graph:
+        _kernel_table(runner.graphs[key], args.kernel_table, rank, barrier)
 
     # time per output token inside the timed end-to-end window (one-off costs such as the first
     # capture of a decode graph and the wait behind other requests' prefill chunks are in TTFT)

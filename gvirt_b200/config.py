@@ -307,7 +307,7 @@ class EnvFlags:
     a2a_scratch_gb: float = 16.0         # GVIRT_A2A_SCRATCH_GB: cap on the slot-addressed MoE exchange buffers
     async_scheduling: bool = True        # GVIRT_ASYNC_SCHEDULING: prepare step k + 1 on the host during step k
     symm_max_bytes: int = 8 << 20        # GVIRT_SYMM_MAX_BYTES: largest payload of the own collectives
-    sp_max_ranks: int = 2                # GVIRT_SP_MAX_RANKS: sequence-parallel layer loop up to this TP size
+    sp_max_ranks: int = 8                # GVIRT_SP_MAX_RANKS: sequence-parallel layer loop up to this TP size
     prefill_gemm_persistent: int = 3     # GVIRT_PREFILL_GEMM_PERSISTENT: GEMMs with >= 1024 rows through a persistent
                                          # kernel with a double-buffered accumulator: 0 = never, 1 = the grouped kernel
                                          # with one segment (128 x 128 tiles, bias-free only), 2 = token-major 128 x 256

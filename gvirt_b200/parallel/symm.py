@@ -149,7 +149,7 @@ class SymmetricHeap:
     def can_fuse_ag_gemm(self, x_local: torch.Tensor, w: torch.Tensor) -> bool:
         m_r = x_local.shape[0]
         return (not env_flags().disable_symm and x_local.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
-                and m_r % 128 == 0
+                and m_r % 128 == 0 and w.shape[0] % 8 == 0
                 and x_local.shape[1] % 8 == 0 and m_r <= self.sp_rows_cap and x_local.is_contiguous())
 
     # ------------------------------------------------------------------ sequence-parallel fused GEMMs

@@ -260,7 +260,7 @@ def mode_gemm_sp_gpu(world):
     heap, r, dev = ctx.symm, ctx.rank, ctx.device
     # the last two: a feature count that leaves a partial 256-wide tile, and more tiles than SMs
     for (M, N, Kfull) in [(128 * world, 256, 512), (1024 * world // 2, 4096, 4096), (256 * world, 1024, 2048),
-                          (256 * world, 336, 1024), (2048 * world, 4096, 2048)]:
+                          (256 * world, 1344, 1024), (2048 * world, 4096, 2048)]:
         K = Kfull // world
         g = torch.Generator(device=dev).manual_seed(17)
         xf = (torch.randn(M, Kfull, device=dev, generator=g) * 0.5).bfloat16()
