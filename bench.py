@@ -63,6 +63,7 @@ def parse():
 
 def _kernel_table(graph, path, rank, barrier, reps=4):
     """Per-kernel device time of the captured decode step on rank 0 (every rank replays)."""
+    import torch
     from torch.profiler import ProfilerActivity, profile
     barrier()
     with profile(activities=[ProfilerActivity.CUDA]) as prof:

@@ -296,6 +296,9 @@ class EnvFlags:
     fuse_swiglu: bool = True             # GVIRT_FUSE_SWIGLU: SwiGLU in the gate/up GEMM epilogue
     decode_l2_prefetch: bool = False     # GVIRT_DECODE_L2_PREFETCH: a decode GEMM warms L2 with the next GEMM's first
                                          # tiles (measured: +3.6 us per Llama-3-8B layer at TP1, so off)
+    tp_pdl: bool = False                 # GVIRT_TP_PDL: keep programmatic dependent launch on under tensor
+                                         # parallelism (measured slower across GPUs: Llama-3-8B TP4 16.5 k
+                                         # tok/s with it, 21.5 k without)
     fused_ar_residual: bool = True       # GVIRT_FUSED_AR_RESIDUAL: under TP the fused GEMM + all-reduce also adds the
                                          # residual and emits the RMSNorm sums of squares (false: a small kernel behind it)
     prefill_attn_tc: bool = True         # GVIRT_PREFILL_ATTN_TC: tcgen05 flash attention for 128-wide heads
@@ -341,6 +344,7 @@ class EnvFlags:
         f.fused_decode = parse_bool(e.get("GVIRT_FUSED_DECODE"), f.fused_decode)
         f.prefill_attn_tc = parse_bool(e.get("GVIRT_PREFILL_ATTN_TC"), f.prefill_attn_tc)
         f.fused_ar_residual = parse_bool(e.get("GVIRT_FUSED_AR_RESIDUAL"), f.fused_ar_residual)
+        f.tp_pdl = parse_bool(e.get("GVIRT_TP_PDL"), f.tp_pdl)
         f.decode_l2_prefetch = parse_bool(e.get("GVIRT_DECODE_L2_PREFETCH"), f.decode_l2_prefetch)
         f.mla_attn_tc = parse_bool(e.get("GVIRT_MLA_ATTN_TC"), f.mla_attn_tc)
         f.dsa_indexer_tc = parse_bool(e.get("GVIRT_DSA_INDEXER_TC"), f.dsa_indexer_tc)

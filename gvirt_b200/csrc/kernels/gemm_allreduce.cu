@@ -229,7 +229,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 2)
 gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                       const __grid_constant__ CUtensorMap tmNext, bf16* out, const bf16* __restrict__ bias,
                       const bf16* residual, int N, int M, int K, long long ldo, int splitk, ArArgs a,
-                      NextWeights next, unsigned int* status) {
+                      NextWeights next, int early_trigger, unsigned int* status) {
   using C = Cfg<BN, 108>;
   extern __shared__ uint8_t smem_raw[];
   const Shared sh = carve<C>(smem_raw);
@@ -244,7 +244,7 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
 
   // weights (P) are constant and are prefetched before the wait on the kernel in front
   if (next.stages > 0) next.tm = &tmNext;
-  const uint32_t tmem_base = run_mainloop<C>(sh, &tmW, &tmX, p0, 0, kb0, nkb, status, -1, -1, 1, &next);
+  const uint32_t tmem_base = run_mainloop<C>(sh, &tmW, &tmX, p0, 0, kb0, nkb, status, -1, -1, early_trigger ? 1 : 2, &next);
   // the channel generation is bumped by the previous user of the channel: read it after the wait
   const unsigned int gen = *reinterpret_cast<volatile unsigned int*>(&a.state[0]) + 1u;
 
@@ -406,6 +406,19 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
   }
 }
 
+// How the fused GEMM + all-reduce takes part in programmatic dependent launch (GVIRT_AR_PDL):
+// bit 0 = the kernel itself may start before the kernel in front has drained, bit 1 = it lets the
+// kernel behind it start early. Across GPUs the kernel's push phase is on every peer's critical
+// path, so what shares the SMs and HBM with it matters more than on one GPU.
+static int ar_pdl_mode() {
+  static int mode = -1;
+  if (mode < 0) {
+    const char* e = getenv("GVIRT_AR_PDL");
+    mode = (e != nullptr && e[0] >= '0' && e[0] <= '3') ? e[0] - '0' : 3;
+  }
+  return mode;
+}
+
 template <int BN>
 static int launch_ar(const CUtensorMap& tmW, const CUtensorMap& tmX, bf16* out, const bf16* bias,
                      const bf16* residual, int N, int M, int K, long long ldo, int splitk,
@@ -438,7 +451,7 @@ static int launch_ar(const CUtensorMap& tmW, const CUtensorMap& tmX, bf16* out, 
     attr[na].val.clusterDim.z = (unsigned)splitk;
     ++na;
   }
-  if (pdl_enabled()) {
+  if (pdl_enabled() && (ar_pdl_mode() & 1)) {
     attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[na].val.programmaticStreamSerializationAllowed = 1;
     ++na;
@@ -446,7 +459,7 @@ static int launch_ar(const CUtensorMap& tmW, const CUtensorMap& tmX, bf16* out, 
   cfg.attrs = attr;
   cfg.numAttrs = na;
   cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmW, tmX, tmNext, out, bias, residual, N, M, K, ldo, splitk,
-                                     a, next, status_word());
+                                     a, next, (ar_pdl_mode() >> 1) & 1, status_word());
   if (e != cudaSuccess) {
     set_last_error("gemm_allreduce: launch", e);
     return GV_ECUDA;

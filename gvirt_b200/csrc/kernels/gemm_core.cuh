@@ -91,7 +91,7 @@ __device__ __forceinline__ uint32_t run_mainloop(const Shared& sh, const CUtenso
                                                  const NextWeights* next = nullptr) {
   constexpr int BN = C::BN;
   const int warp = threadIdx.x >> 5;
-  if (pdl_dep) pdl_trigger();
+  if (pdl_dep == 1) pdl_trigger();   // 2: dependent launch without the early trigger
   if (warp == 0 && sm100::elect_one()) {
     sm100::tma_prefetch_desc(tmP);
     sm100::tma_prefetch_desc(tmQ);
