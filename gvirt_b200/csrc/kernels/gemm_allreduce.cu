@@ -244,7 +244,7 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
 
   // weights (P) are constant and are prefetched before the wait on the kernel in front
   if (next.stages > 0) next.tm = &tmNext;
-  const uint32_t tmem_base = run_mainloop<C>(sh, &tmW, &tmX, p0, 0, kb0, nkb, status, -1, -1, early_trigger ? 1 : 2, &next);
+  const uint32_t tmem_base = run_mainloop<C>(sh, &tmW, &tmX, p0, 0, kb0, nkb, status, -1, -1, early_trigger ? 1 : 3, &next);
   // the channel generation is bumped by the previous user of the channel: read it after the wait
   const unsigned int gen = *reinterpret_cast<volatile unsigned int*>(&a.state[0]) + 1u;
 

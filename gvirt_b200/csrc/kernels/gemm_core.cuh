@@ -82,16 +82,18 @@ __device__ __forceinline__ Shared carve(uint8_t* raw) {
 // and Q is produced by the kernel in front; 2 = the reverse. With 1 or 2 the set-up and the first
 // ring-full of constant-operand tiles are fetched BEFORE waiting for the predecessor, so weight
 // streaming starts while the previous kernel drains; every thread has waited by the time
-// run_mainloop returns.
+// run_mainloop returns. 3 = as 1 without the early trigger for the kernel behind.
 template <class C>
 __device__ __forceinline__ uint32_t run_mainloop(const Shared& sh, const CUtensorMap* tmP,
                                                  const CUtensorMap* tmQ, int p0, int q0, int kb0,
                                                  int nkb, unsigned int* status, int pz = -1,
-                                                 int qz = -1, int pdl_dep = 0,
+                                                 int qz = -1, int pdl_mode = 0,
                                                  const NextWeights* next = nullptr) {
   constexpr int BN = C::BN;
   const int warp = threadIdx.x >> 5;
-  if (pdl_dep == 1) pdl_trigger();   // 2: dependent launch without the early trigger
+  // 3 = as 1, but the kernel behind this one is not let in early
+  const int pdl_dep = pdl_mode == 3 ? 1 : pdl_mode;
+  if (pdl_mode == 1 || pdl_mode == 2) pdl_trigger();
   if (warp == 0 && sm100::elect_one()) {
     sm100::tma_prefetch_desc(tmP);
     sm100::tma_prefetch_desc(tmQ);
