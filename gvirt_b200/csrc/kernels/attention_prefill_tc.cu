@@ -36,11 +36,9 @@ namespace fa {
 
 constexpr int HD = 128;
 constexpr int BM = 128;             // query rows per CTA
-constexpr int BN = 128;             // keys per tile
-constexpr int TILE_BYTES = 128 * 128 * 2;   // one 128 x 128 bf16 tile = two 64-column chunks
-constexpr int CHUNK_BYTES = 128 * 128;      // 128 rows x 128 bytes
+constexpr int Q_BYTES = 128 * 128 * 2;      // the Q tile: 128 rows x 128 features = two 64-column chunks
+constexpr int CHUNK128 = 128 * 128;         // 128 rows x 128 bytes: one chunk of Q and of P
 constexpr int KV_STAGES = 2;
-constexpr int TMEM_COLS = 512;      // S0 [0,128) S1 [128,256) O [256,384)
 constexpr float RESCALE_LOG2 = 8.f; // move the running maximum only past this gap (log2 units)
 
 struct Bars {
@@ -52,22 +50,48 @@ struct Bars {
   uint32_t tmem_slot;
 };
 
-constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 * KV_STAGES + 1) + 1024 + sizeof(Bars) + 3 * 256 * 4;
+// Two shapes of the kernel. BN = keys per tile:
+//   BN = 128: one CTA per SM (Q 32 KB + 2 x (K + V) 128 KB + P 32 KB), S0 | S1 | O = 384 TMEM columns
+//             (512 allocated), one or two softmax warp groups.
+//   BN = 64:  two CTAs per SM (Q 32 KB + 2 x (K + V) 64 KB + P 16 KB = 112 KB each), S0 | S1 | O = 256
+//             columns each. While one CTA's softmax warps exponentiate, the other CTA's MMAs run, and a
+//             CTA's fixed part (set-up, first tile, epilogue) hides behind its neighbour's tiles.
+template <int BN>
+struct Shape {
+  static constexpr int KV_BYTES = BN * 128 * 2;       // one K or V tile: BN keys x 128 features
+  static constexpr int KV_CHUNK = BN * 128;           // BN key rows x 128 bytes (64 features)
+  static constexpr int P_BYTES = BM * BN * 2;         // BN / 64 chunks of 128 rows x 128 bytes
+  static constexpr int TMEM_COLS = BN == 128 ? 512 : 256;   // S0 [0, BN) S1 [BN, 2 BN) O [2 BN, 2 BN + 128)
+  static constexpr int XCH_BYTES = BN == 128 ? 3 * 256 * 4 : 0;   // two-warp-group exchange (BN = 128 only)
+  static constexpr int SMEM_BYTES = Q_BYTES + 2 * KV_STAGES * KV_BYTES + P_BYTES + 256 + XCH_BYTES
+                                    + (BN == 128 ? 1024 : 0);     // BN = 64 relies on the declared alignment
+};
+static_assert(sizeof(Bars) <= 256, "barrier block");
 
-template <int WG>
-__global__ void __launch_bounds__(64 + 128 * WG, 1)
+template <int WG, int BN>
+__global__ void __launch_bounds__(64 + 128 * WG, BN == 128 ? 1 : 2)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const int* __restrict__ block_tables,
                   const int* __restrict__ q_start, const int* __restrict__ cached_lens,
                   bf16* __restrict__ out, int nq, int nkv, int block_size, int max_blocks,
                   float scale_log2, long long num_blocks, unsigned int* status) {
-  extern __shared__ uint8_t smem_raw[];
+  using SH = Shape<BN>;
+  constexpr int KV_BYTES = SH::KV_BYTES, KV_CHUNK = SH::KV_CHUNK, TMEM_COLS = SH::TMEM_COLS;
+  static_assert(WG == 1 || BN == 128, "two softmax warp groups only with 128-key tiles");
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  if (BN != 128 && base != smem_raw) {
+    // the 64-key shape has no room for alignment slack: refuse to run misaligned (never observed:
+    // the dynamic window starts on a 1 KB boundary when the kernel has no static shared memory)
+    if (threadIdx.x == 0) atomicOr(status, GV_ST_BAD_INDEX);
+    return;
+  }
   uint8_t* q_s = base;
-  uint8_t* k_s = q_s + TILE_BYTES;                       // [KV_STAGES]
-  uint8_t* v_s = k_s + KV_STAGES * TILE_BYTES;           // [KV_STAGES]
-  uint8_t* p_s = v_s + KV_STAGES * TILE_BYTES;
-  Bars* bars = reinterpret_cast<Bars*>(p_s + TILE_BYTES);
+  uint8_t* k_s = q_s + Q_BYTES;                          // [KV_STAGES]
+  uint8_t* v_s = k_s + KV_STAGES * KV_BYTES;             // [KV_STAGES]
+  uint8_t* p_s = v_s + KV_STAGES * KV_BYTES;
+  Bars* bars = reinterpret_cast<Bars*>(p_s + SH::P_BYTES);
+  float* xch_base = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 256);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int b = blockIdx.z, h = blockIdx.y;
@@ -109,14 +133,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   __syncthreads();
   sm100::tc_fence_after();
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_slot);
-  const uint32_t tmem_o = tmem + 256;
+  const uint32_t tmem_o = tmem + 2 * BN;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (sm100::elect_one()) {
-      sm100::mbar_expect_tx(&bars->q_full, TILE_BYTES);
+      sm100::mbar_expect_tx(&bars->q_full, Q_BYTES);
       for (int c = 0; c < 2; ++c)
-        sm100::tma_load_2d(q_s + c * CHUNK_BYTES, &tmQ, &bars->q_full, h * HD + c * 64, qs0 + q_lo);
+        sm100::tma_load_2d(q_s + c * CHUNK128, &tmQ, &bars->q_full, h * HD + c * 64, qs0 + q_lo);
       const int rows_per_box = block_size < BN ? block_size : BN;
       const int boxes = BN / rows_per_box;
       for (int t = 0; t < ntiles; ++t) {
@@ -126,14 +150,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         for (int kv = 0; kv < 2 && ok; ++kv) {
           uint64_t* full = kv == 0 ? &bars->k_full[s] : &bars->v_full[s];
           uint64_t* empty = kv == 0 ? &bars->k_empty[s] : &bars->v_empty[s];
-          uint8_t* dst = (kv == 0 ? k_s : v_s) + s * TILE_BYTES;
+          uint8_t* dst = (kv == 0 ? k_s : v_s) + s * KV_BYTES;
           const CUtensorMap* tm = kv == 0 ? &tmK : &tmV;
           if (!sm100::mbar_wait(empty, ph ^ 1u)) {
             atomicOr(status, GV_ST_TIMEOUT_TMA);
             ok = false;
             break;
           }
-          sm100::mbar_expect_tx(full, TILE_BYTES);
+          sm100::mbar_expect_tx(full, KV_BYTES);
           for (int bx = 0; bx < boxes; ++bx) {
             const int pos = t * BN + bx * rows_per_box;
             // keys past the end of the sequence are masked by the softmax; a block-table entry
@@ -146,7 +170,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             }
             const int row = blk * block_size + pos % block_size;
             for (int c = 0; c < 2; ++c)
-              sm100::tma_load_2d(dst + c * CHUNK_BYTES + bx * rows_per_box * 128, tm, full,
+              sm100::tma_load_2d(dst + c * KV_CHUNK + bx * rows_per_box * 128, tm, full,
                                  kvh * HD + c * 64, row);
           }
         }
@@ -170,12 +194,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           return false;
         }
         sm100::tc_fence_after();
-        const uint32_t qa = sm100::smem_u32(q_s), ka = sm100::smem_u32(k_s + s * TILE_BYTES);
+        const uint32_t qa = sm100::smem_u32(q_s), ka = sm100::smem_u32(k_s + s * KV_BYTES);
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
-          const uint32_t off = (uint32_t)(k >> 2) * CHUNK_BYTES;
-          sm100::mma_f16_ss(tmem + sb * 128, sm100::smem_desc_sw128(qa + off) + (uint64_t)(2 * (k & 3)),
-                            sm100::smem_desc_sw128(ka + off) + (uint64_t)(2 * (k & 3)), idesc_qk,
+          sm100::mma_f16_ss(tmem + sb * BN,
+                            sm100::smem_desc_sw128(qa + (uint32_t)(k >> 2) * CHUNK128) + (uint64_t)(2 * (k & 3)),
+                            sm100::smem_desc_sw128(ka + (uint32_t)(k >> 2) * KV_CHUNK) + (uint64_t)(2 * (k & 3)), idesc_qk,
                             (uint32_t)(k != 0));
         }
         sm100::tc_commit(&bars->k_empty[s]);
@@ -194,13 +218,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           break;
         }
         sm100::tc_fence_after();
-        const uint32_t pa = sm100::smem_u32(p_s), va = sm100::smem_u32(v_s + s * TILE_BYTES);
+        const uint32_t pa = sm100::smem_u32(p_s), va = sm100::smem_u32(v_s + s * KV_BYTES);
 #pragma unroll
         for (int k = 0; k < BN / 16; ++k) {
           // A = P [128 rows x 16 keys] K-major; B = V [16 keys x 128 features] as it lies in the
           // tile: key rows of 128 bytes, the second 64 features one chunk further
-          const uint64_t da = sm100::smem_desc_sw128(pa + (uint32_t)(k >> 2) * CHUNK_BYTES) + (uint64_t)(2 * (k & 3));
-          const uint64_t db = sm100::smem_desc_mn_sw128(va + (uint32_t)k * 2048u, CHUNK_BYTES, 1024);
+          const uint64_t da = sm100::smem_desc_sw128(pa + (uint32_t)(k >> 2) * CHUNK128) + (uint64_t)(2 * (k & 3));
+          const uint64_t db = sm100::smem_desc_mn_sw128(va + (uint32_t)k * 2048u, KV_CHUNK, 1024);
           sm100::mma_f16_ss(tmem_o, da, db, idesc_pv, (uint32_t)((t | k) != 0));
         }
         sm100::tc_commit(&bars->v_empty[s]);
@@ -219,7 +243,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
     const int qi = q_lo + r;                           // token index inside the request
     const int limit = min(cached + qi, kv_end - 1);    // last visible key of this row
-    float* xch = reinterpret_cast<float*>(bars + 1);   // [2][128] row maxima / sums of the two halves
+    float* xch = xch_base;                             // [2][128] row maxima / sums of the two halves
     auto pair_bar = [&]() {                            // the two warps that share this row range
       if (WG == 2) asm volatile("bar.sync %0, 64;" ::"r"(2 + quad) : "memory");
     };
@@ -236,25 +260,25 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       float sv[COLS];
 #pragma unroll
       for (int c = 0; c < COLS; c += 32)
-        sm100::tmem_ld32(tmem + lane_addr + sb * 128 + half * COLS + c, reinterpret_cast<uint32_t*>(sv + c));
+        sm100::tmem_ld32(tmem + lane_addr + sb * BN + half * COLS + c, reinterpret_cast<uint32_t*>(sv + c));
       sm100::tmem_ld_wait();
       sm100::tc_fence_before();
       sm100::mbar_arrive(&bars->s_empty[sb]);
       const int k0 = t * BN + half * COLS;
+      // sv stays unscaled: the scale (> 0) is applied to the row maximum once and to every score
+      // inside the exponent's multiply-add, so a score costs max + fma + ex2 + add
       float mx = -INFINITY;
       if (t * BN + BN - 1 <= cached + q_lo && t * BN + BN <= kv_end) {
 #pragma unroll
-        for (int j = 0; j < COLS; ++j) {
-          sv[j] *= scale_log2;
-          mx = fmaxf(mx, sv[j]);
-        }
+        for (int j = 0; j < COLS; ++j) mx = fmaxf(mx, sv[j]);
       } else {
 #pragma unroll
         for (int j = 0; j < COLS; ++j) {
-          sv[j] = (k0 + j <= limit) ? sv[j] * scale_log2 : -INFINITY;
+          sv[j] = (k0 + j <= limit) ? sv[j] : -INFINITY;
           mx = fmaxf(mx, sv[j]);
         }
       }
+      mx *= scale_log2;
       if (WG == 2) {                                   // row maximum over both halves
         xch[(t & 1) * 256 + half * 128 + r] = mx;
         pair_bar();
@@ -266,7 +290,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       bool waited = false;
       if (any_grow) {
         const float m_new = grow ? mx : m;
-        const float f = (m == -INFINITY) ? 0.f : exp2f(m - m_new);
+        const float f = (m == -INFINITY) ? 0.f : sm100::ex2_approx(m - m_new);
         if (t > 0) {
           if (ok && !sm100::mbar_wait(&bars->pv_done, (uint32_t)(t - 1) & 1u)) ok = false;
           waited = true;
@@ -285,12 +309,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         }
         m = m_new;
       }
-      const float mref = (m == -INFINITY) ? 0.f : m;
+      const float nmref = (m == -INFINITY) ? 0.f : -m;
       float rs = 0.f;
       uint32_t pk[COLS / 2];
 #pragma unroll
       for (int j = 0; j < COLS; j += 2) {
-        const float p0 = exp2f(sv[j] - mref), p1 = exp2f(sv[j + 1] - mref);
+        const float p0 = sm100::ex2_approx(fmaf(sv[j], scale_log2, nmref));
+        const float p1 = sm100::ex2_approx(fmaf(sv[j + 1], scale_log2, nmref));
         rs += p0 + p1;
         pk[j >> 1] = pack_bf2(p0, p1);
       }
@@ -299,7 +324,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       // P row r: 64-key chunks, 16-byte pieces XOR-swizzled by (r & 7) like a TMA tile
 #pragma unroll
       for (int c = 0; c < COLS / 64; ++c) {
-        uint8_t* row = p_s + (half * (COLS / 64) + c) * CHUNK_BYTES + r * 128;
+        uint8_t* row = p_s + (half * (COLS / 64) + c) * CHUNK128 + r * 128;
 #pragma unroll
         for (int piece = 0; piece < 8; ++piece) {
           const int i = c * 32 + piece * 4;
@@ -352,10 +377,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 
 using namespace gv;
 
-// Softmax warp groups of the tcgen05 prefill attention kernel: 1 (one thread per query row) or 2
-// (two threads per row, one 64-key half each).
+// Shape of the tcgen05 prefill attention kernel: 1 = 128-key tiles, one softmax warp group (one
+// thread per query row); 2 = 128-key tiles, two warp groups (two threads per row, one 64-key half
+// each); 4 = 64-key tiles, two CTAs per SM.
 static long long g_prefill_tc_wg = 2;
-extern "C" void gv_set_prefill_tc_warpgroups(long long wg) { g_prefill_tc_wg = wg == 2 ? 2 : 1; }
+extern "C" void gv_set_prefill_tc_warpgroups(long long wg) {
+  g_prefill_tc_wg = (wg == 1 || wg == 2 || wg == 4) ? wg : 2;
+}
 
 // Same arguments as gv_paged_attention_prefill plus `total_tokens` (rows of q / out). head_dim
 // must be 128 and block_size a power of two in [8, ...] that divides or is a multiple of 128;
@@ -373,6 +401,7 @@ extern "C" int gv_paged_attention_prefill_tc(const void* q, const void* k_cache,
   if (batch == 0 || max_q_len == 0 || total_tokens == 0) return GV_OK;
   if (nkv <= 0 || nq % nkv != 0) return GV_EINVAL;
   if (head_dim != 128) return GV_EUNSUPPORTED;
+  if (!(scale > 0.f)) return GV_EINVAL;              // the kernel scales the row maximum, not every score
   if (block_size < 8 || (block_size & (block_size - 1)) != 0) return GV_EUNSUPPORTED;
   if (batch > 65535 || nq > 65535) return GV_ETOOBIG;
   if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_cache) |
@@ -381,17 +410,21 @@ extern "C" int gv_paged_attention_prefill_tc(const void* q, const void* k_cache,
   CUtensorMap tmQ, tmK, tmV;
   int rc;
   const long long kv_rows = num_blocks * block_size;
-  const int box = block_size < 128 ? (int)block_size : 128;
+  const int bn = g_prefill_tc_wg == 4 ? 64 : 128;
+  const int box = block_size < bn ? (int)block_size : bn;
   if ((rc = gemm::cached_tmap_bf16(&tmQ, q, total_tokens, nq * 128, nq * 128, 128)) != GV_OK) return rc;
   if ((rc = gemm::cached_tmap_bf16(&tmK, k_cache, kv_rows, nkv * 128, nkv * 128, box)) != GV_OK) return rc;
   if ((rc = gemm::cached_tmap_bf16(&tmV, v_cache, kv_rows, nkv * 128, nkv * 128, box)) != GV_OK) return rc;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(fa::prefill_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         fa::SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(fa::prefill_tc_kernel<1, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         fa::Shape<128>::SMEM_BYTES);
     if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(fa::prefill_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               fa::SMEM_BYTES);
+      e = cudaFuncSetAttribute(fa::prefill_tc_kernel<2, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               fa::Shape<128>::SMEM_BYTES);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(fa::prefill_tc_kernel<1, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               fa::Shape<64>::SMEM_BYTES);
     if (e != cudaSuccess) {
       set_last_error("prefill_tc: smem attr", e);
       return GV_ECUDA;
@@ -399,15 +432,16 @@ extern "C" int gv_paged_attention_prefill_tc(const void* q, const void* k_cache,
     configured = true;
   }
   dim3 grid((unsigned)((max_q_len + fa::BM - 1) / fa::BM), (unsigned)nq, (unsigned)batch);
-  if (g_prefill_tc_wg == 2)
-    fa::prefill_tc_kernel<2><<<grid, 64 + 256, fa::SMEM_BYTES, (cudaStream_t)stream>>>(
-        tmQ, tmK, tmV, (const int*)block_tables, (const int*)q_start, (const int*)cached_lens, (bf16*)out,
-        (int)nq, (int)nkv, (int)block_size, (int)max_blocks, scale * 1.4426950408889634f, num_blocks,
-        status_word());
+  const float sl2 = scale * 1.4426950408889634f;
+  cudaStream_t st = (cudaStream_t)stream;
+#define GV_PF_ARGS tmQ, tmK, tmV, (const int*)block_tables, (const int*)q_start, (const int*)cached_lens, \
+                   (bf16*)out, (int)nq, (int)nkv, (int)block_size, (int)max_blocks, sl2, num_blocks, status_word()
+  if (g_prefill_tc_wg == 4)
+    fa::prefill_tc_kernel<1, 64><<<grid, 64 + 128, fa::Shape<64>::SMEM_BYTES, st>>>(GV_PF_ARGS);
+  else if (g_prefill_tc_wg == 2)
+    fa::prefill_tc_kernel<2, 128><<<grid, 64 + 256, fa::Shape<128>::SMEM_BYTES, st>>>(GV_PF_ARGS);
   else
-    fa::prefill_tc_kernel<1><<<grid, 64 + 128, fa::SMEM_BYTES, (cudaStream_t)stream>>>(
-        tmQ, tmK, tmV, (const int*)block_tables, (const int*)q_start, (const int*)cached_lens, (bf16*)out,
-        (int)nq, (int)nkv, (int)block_size, (int)max_blocks, scale * 1.4426950408889634f, num_blocks,
-        status_word());
+    fa::prefill_tc_kernel<1, 128><<<grid, 64 + 128, fa::Shape<128>::SMEM_BYTES, st>>>(GV_PF_ARGS);
+#undef GV_PF_ARGS
   return check_launch("paged_prefill_tc");
 }

@@ -231,17 +231,20 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       sm100::mbar_arrive(&bars->s_empty[sb]);
       const int k0 = start + t * BN;
       float mx = -INFINITY;
+      // sv stays unscaled: the scale (> 0) goes onto the row maximum once and into the exponent's
+      // multiply-add
 #pragma unroll
       for (int j = 0; j < BN; ++j) {
-        sv[j] = (k0 + j < end) ? sv[j] * scale_log2 : -INFINITY;
+        sv[j] = (k0 + j < end) ? sv[j] : -INFINITY;
         mx = fmaxf(mx, sv[j]);
       }
+      mx *= scale_log2;
       const bool grow = mx > m + RESCALE_LOG2;
       const bool any_grow = __any_sync(0xffffffffu, grow);
       bool waited = false;
       if (any_grow) {
         const float m_new = grow ? mx : m;
-        const float f = (m == -INFINITY) ? 0.f : exp2f(m - m_new);
+        const float f = (m == -INFINITY) ? 0.f : sm100::ex2_approx(m - m_new);
         if (t > 0) {
           if (ok && !sm100::mbar_wait(&bars->pv_done, (uint32_t)(t - 1) & 1u)) ok = false;
           waited = true;
@@ -260,12 +263,13 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         }
         m = m_new;
       }
-      const float mref = (m == -INFINITY) ? 0.f : m;
+      const float nmref = (m == -INFINITY) ? 0.f : -m;
       float rs = 0.f;
       uint32_t pk[BN / 2];
 #pragma unroll
       for (int j = 0; j < BN; j += 2) {
-        const float p0 = exp2f(sv[j] - mref), p1 = exp2f(sv[j + 1] - mref);
+        const float p0 = sm100::ex2_approx(fmaf(sv[j], scale_log2, nmref));
+        const float p1 = sm100::ex2_approx(fmaf(sv[j + 1], scale_log2, nmref));
         rs += p0 + p1;
         pk[j >> 1] = pack_bf2(p0, p1);
       }
@@ -351,6 +355,7 @@ extern "C" int gv_mla_attention_tc(const void* qf, const void* cache, const void
                                    long long block_size, long long max_blocks, long long nsplit,
                                    float scale, long long num_blocks, void* stream) {
   if (!qf || !cache || !block_tables || !seq_lens || !out) return GV_EINVAL;
+  if (!(scale > 0.f)) return GV_EINVAL;              // the kernel scales the row maximum, not every score
   if (batch == 0) return GV_OK;
   if (dc != mlatc::DC || dr != mlatc::DR || heads % mlatc::HEADS != 0 || block_size % mlatc::BN != 0)
     return GV_EUNSUPPORTED;

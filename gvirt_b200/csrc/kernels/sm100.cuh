@@ -195,6 +195,15 @@ __device__ __forceinline__ void tmem_st_wait() {
 }
 // Makes shared-memory writes of the generic proxy (plain stores) visible to the async proxy
 // (tcgen05.mma operand reads, TMA stores). Every writing thread issues it before signalling.
+// 2^x on the special-function unit in one instruction (exp2f() wraps the same instruction in a
+// range fix-up for denormal results, several instructions per call; the softmax loops flush those
+// to zero anyway). ex2(-inf) = +0.
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }

@@ -15,11 +15,11 @@ from tests.test_gpu_attention import build
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
-DEFAULT_WG = 2
+DEFAULT_WG = 2      # 64-key tiles, two CTAs per SM; 1 / 2 = 128-key tiles with one / two softmax warp groups
 
 
 def _tc(q, kc, vc, m, nq, nkv, hd, bs, wg=None):
-    """`wg`: softmax warp groups of the kernel (1 or 2); None keeps the library default."""
+    """`wg`: shape of the kernel (1, 2 or 4, see DEFAULT_WG); None keeps the library default."""
     out = torch.empty_like(q)
     lib = _native.kernels()
     if wg is not None:
@@ -66,9 +66,9 @@ def test_prefill_tc_block_sizes_and_groups(bs, nq, nkv):
     cached = [0, 0, 5, 130, 0, 900, 64]
     q, kc, vc, mc, m = build(lens, cached, nq, nkv, hd, bs, seed=bs + nq)
     want = ref.paged_attention(q, kc, vc, mc.block_tables, mc.query_start_loc, mc.cached_lens, nq, nkv, hd, bs)
-    for wg in (1, 2):
+    for wg in (1, 2, 4):
         got = _tc(q.to(DEV), kc.to(DEV), vc.to(DEV), m, nq, nkv, hd, bs, wg=wg)
-        close(got, want, atol=1e-2, rtol=2e-2, what=f"prefill tc bs={bs} {nq}/{nkv} warp groups={wg}")
+        close(got, want, atol=1e-2, rtol=2e-2, what=f"prefill tc bs={bs} {nq}/{nkv} shape={wg}")
     status_ok()
 
 
@@ -87,7 +87,7 @@ def test_prefill_tc_forces_lazy_rescale_of_the_output():
             kc[blk] = (kc[blk].float() * (0.2 + pos / 40.0)[:, None, None]).bfloat16()
     q = (q.float() * 3).bfloat16()
     want = ref.paged_attention(q, kc, vc, mc.block_tables, mc.query_start_loc, mc.cached_lens, nq, nkv, hd, bs)
-    for wg in (1, 2):
+    for wg in (1, 2, 4):
         got = _tc(q.to(DEV), kc.to(DEV), vc.to(DEV), m, nq, nkv, hd, bs, wg=wg)
         close(got, want, atol=2e-2, rtol=2e-2, what=f"prefill tc with rescaling, warp groups={wg}")
     status_ok()
@@ -113,7 +113,7 @@ def test_prefill_tc_32769_tokens():
     nq, nkv, hd, bs = 2, 1, 128, 128
     q, kc, vc, mc, m = build([32769], [0], nq, nkv, hd, bs, seed=2)
     want = _ref_gpu(q, kc, vc, mc, nq, nkv, hd, bs)
-    for wg in (1, 2):
+    for wg in (1, 2, 4):
         got = _tc(q.to(DEV), kc.to(DEV), vc.to(DEV), m, nq, nkv, hd, bs, wg=wg)
         close(got, want, atol=1e-2, rtol=2e-2, what=f"32769-token prefill, warp groups={wg}")
     status_ok()
