@@ -11,12 +11,17 @@
 //     and the paged caches: a 128-key tile is `128 / block_size` boxes addressed through the
 //     block table, 128-byte swizzled, no register staging;
 //   * S = Q K^T and O += P V are tcgen05.mma with fp32 accumulators in tensor memory (S double
-//     buffered: 2 x 128 columns, O: 128 columns). The V tile is consumed where TMA put it, as an
-//     MN-major B operand, so no transposed copy of V exists anywhere;
-//   * warp roles: warp 0 issues TMA, warp 1 issues every MMA, warps 2-5 run the softmax, one
-//     thread per query row (its TMEM lane): row maxima and sums need no shuffles. The MMA warp
+//     buffered, then O: 128 columns). The V tile is consumed where TMA put it, as an MN-major B
+//     operand, so no transposed copy of V exists anywhere;
+//   * warp roles: warp 0 issues TMA, warp 1 issues every MMA, the other warps run the softmax,
+//     one thread per query row (its TMEM lane): row maxima and sums need no shuffles. The MMA warp
 //     issues Q K^T of tile t + 1 before it waits for P of tile t, so the tensor core works
 //     while the softmax warps exponentiate;
+//   * a score costs four instructions: the row maximum is taken on the raw accumulator and scaled
+//     once, the softmax scale rides in the multiply-add that forms the exponent, and 2^x is the
+//     special-function instruction itself (`ex2.approx`);
+//   * two shapes (`Shape<BN>` below): 128-key tiles with one CTA per SM, or 64-key tiles with two
+//     CTAs per SM, where one CTA's MMAs and fixed parts overlap the other's softmax;
 //   * lazy rescaling: the running maximum only moves when a tile exceeds it by more than 2^8,
 //     so O is read back and scaled (tcgen05.ld / tcgen05.st) for a handful of tiles only.
 //
@@ -380,9 +385,9 @@ using namespace gv;
 // Shape of the tcgen05 prefill attention kernel: 1 = 128-key tiles, one softmax warp group (one
 // thread per query row); 2 = 128-key tiles, two warp groups (two threads per row, one 64-key half
 // each); 4 = 64-key tiles, two CTAs per SM.
-static long long g_prefill_tc_wg = 2;
+static long long g_prefill_tc_wg = 4;
 extern "C" void gv_set_prefill_tc_warpgroups(long long wg) {
-  g_prefill_tc_wg = (wg == 1 || wg == 2 || wg == 4) ? wg : 2;
+  g_prefill_tc_wg = (wg == 1 || wg == 2 || wg == 4) ? wg : 4;
 }
 
 // Same arguments as gv_paged_attention_prefill plus `total_tokens` (rows of q / out). head_dim

@@ -15,7 +15,7 @@ from tests.test_gpu_attention import build
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
-DEFAULT_WG = 2      # 64-key tiles, two CTAs per SM; 1 / 2 = 128-key tiles with one / two softmax warp groups
+DEFAULT_WG = 4      # 64-key tiles, two CTAs per SM; 1 / 2 = 128-key tiles with one / two softmax warp groups
 
 
 def _tc(q, kc, vc, m, nq, nkv, hd, bs, wg=None):
