@@ -296,6 +296,9 @@ class EnvFlags:
     fuse_swiglu: bool = True             # GVIRT_FUSE_SWIGLU: SwiGLU in the gate/up GEMM epilogue
     decode_l2_prefetch: bool = False     # GVIRT_DECODE_L2_PREFETCH: a decode GEMM warms L2 with the next GEMM's first
                                          # tiles (measured: +3.6 us per Llama-3-8B layer at TP1, so off)
+    vocab_parallel_greedy: bool = False  # GVIRT_VOCAB_PARALLEL_GREEDY: all-greedy steps under TP pick the best
+                                         # token per vocabulary shard and all-gather (score, id) pairs
+                                         # instead of the logits
     tp_pdl: bool = False                 # GVIRT_TP_PDL: keep programmatic dependent launch on under tensor
                                          # parallelism (measured slower across GPUs: Llama-3-8B TP4 16.5 k
                                          # tok/s with it, 21.5 k without)
@@ -345,6 +348,7 @@ class EnvFlags:
         f.prefill_attn_tc = parse_bool(e.get("GVIRT_PREFILL_ATTN_TC"), f.prefill_attn_tc)
         f.fused_ar_residual = parse_bool(e.get("GVIRT_FUSED_AR_RESIDUAL"), f.fused_ar_residual)
         f.tp_pdl = parse_bool(e.get("GVIRT_TP_PDL"), f.tp_pdl)
+        f.vocab_parallel_greedy = parse_bool(e.get("GVIRT_VOCAB_PARALLEL_GREEDY"), f.vocab_parallel_greedy)
         f.decode_l2_prefetch = parse_bool(e.get("GVIRT_DECODE_L2_PREFETCH"), f.decode_l2_prefetch)
         f.mla_attn_tc = parse_bool(e.get("GVIRT_MLA_ATTN_TC"), f.mla_attn_tc)
         f.dsa_indexer_tc = parse_bool(e.get("GVIRT_DSA_INDEXER_TC"), f.dsa_indexer_tc)

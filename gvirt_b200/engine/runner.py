@@ -233,7 +233,11 @@ class ModelRunner:
                             stochastic: bool, step_id: int, mm=None, logprobs: int = 0, penalties=None):
         toks = self.dev_tokens[:ntok]
         h = self.model.forward(toks, meta, self.kv_caches, self.ws, mm_override=mm)
-        if want_sample:
+        if (want_sample and not stochastic and penalties is None and logprobs == 0 and self.model.ctx.tp > 1
+                and flags().vocab_parallel_greedy and hasattr(self.model, "greedy_tokens")):
+            # all-greedy step under tensor parallelism: pick the token per vocabulary shard
+            self.dev_out[:rows].copy_(self.model.greedy_tokens(h, meta, self.ws, batch=rows))
+        elif want_sample:
             logits = self.model.compute_logits(h, meta, self.ws, batch=rows)
             if penalties is not None:
                 self._apply_penalties(logits, penalties)

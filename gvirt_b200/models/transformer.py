@@ -428,9 +428,10 @@ class Transformer:
         return h
 
     def compute_logits(self, hidden: torch.Tensor, meta: F.AttnMeta, ws: Optional[Workspace] = None,
-                       batch: Optional[int] = None) -> torch.Tensor:
+                       batch: Optional[int] = None, gather: bool = True) -> torch.Tensor:
         """Logits of each request's last new token: gather rows -> vocab-parallel lm_head ->
-        all-gather over TP (xlite/csrc/model.cpp:1458-1475). Returns [B, V]."""
+        all-gather over TP (xlite/csrc/model.cpp:1458-1475). Returns [B, V]; with `gather=False`
+        this rank's vocabulary shard [B, V / tp] (token ids offset by `vocab_start`)."""
         cfg, ctx = self.cfg, self.ctx
         ws = ws or TorchWorkspace(self.device)
         B = batch if batch is not None else meta.batch
@@ -440,7 +441,7 @@ class Transformer:
         logits = ws.get((B, self.vocab_local), self.dtype)
         F.linear(rows, lm, None, out=logits)
         ws.put(rows)
-        if ctx.tp > 1:
+        if ctx.tp > 1 and gather:
             full = ws.get((ctx.tp, B, self.vocab_local), self.dtype)
             coll.all_gather(logits, ctx.tp_group, ctx, out=full.view(ctx.tp * B, self.vocab_local))
             ws.put(logits)
@@ -450,3 +451,26 @@ class Transformer:
             ws.put(full)
             return merged
         return logits
+
+    def greedy_tokens(self, hidden: torch.Tensor, meta: F.AttnMeta, ws: Optional[Workspace] = None,
+                      batch: Optional[int] = None) -> torch.Tensor:
+        """argmax of the logits without assembling them: every rank takes the best token of its
+        vocabulary shard, the (score, id) pairs (8 bytes per request and rank) are all-gathered and
+        the best pair wins, the lowest rank on a tie, which is what argmax over the concatenated
+        vocabulary returns. Replaces the all-gather of [B, V] logits, their re-ordering and a
+        full-vocabulary pass of the sampler. Returns int32 [B]."""
+        ctx = self.ctx
+        logits = self.compute_logits(hidden, meta, ws, batch, gather=False)
+        if ctx.tp == 1:
+            out = F.sample(logits)
+        else:
+            idx, val = F.sample(logits, index_offset=self.vocab_start, return_scores=True)
+            # rows of 16 bytes (score, id, 0, 0): the push collective moves whole 16-byte lines
+            zero = torch.zeros_like(val, dtype=torch.float32)
+            pair = torch.stack([val.float(), idx.view(torch.float32), zero, zero], 1).contiguous()
+            allp = coll.all_gather(pair, ctx.tp_group, ctx).view(ctx.tp, -1, 4)
+            best = allp[:, :, 0].argmax(0, keepdim=True)                                     # first max = lowest rank
+            out = allp[:, :, 1].contiguous().view(torch.int32).gather(0, best)[0]
+        if getattr(logits, "_gv_off", None) is not None and ws is not None:
+            ws.put(logits)
+        return out

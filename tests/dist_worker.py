@@ -543,9 +543,21 @@ def mode_tp_model_gpu(world):
         err = (first[i] - want).abs().max().item() / max(want.abs().max().item(), 1e-6)
         worst = max(worst, err)
     assert worst <= 0.06, f"first-step logits differ from the fp32 oracle by {worst:.3f} of the largest logit"
+    # (2b) tokens picked per vocabulary shard (16 bytes per request gathered instead of the logits)
+    # must be the tokens picked from the assembled logits
+    from gvirt_b200 import config as gcfg
+    before = gcfg.flags().vocab_parallel_greedy
+    os.environ["GVIRT_VOCAB_PARALLEL_GREEDY"] = "0" if before else "1"
+    gcfg.reload_flags()
+    try:
+        _, outs_other, _ = run()
+    finally:
+        os.environ.pop("GVIRT_VOCAB_PARALLEL_GREEDY", None)
+        gcfg.reload_flags()
+    assert outs_other == outs, ("token selection per vocabulary shard differs from selection on gathered logits",
+                                outs, outs_other)
     # (3) library path on the same weights
     os.environ["GVIRT_DISABLE_SYMM"] = "1"
-    from gvirt_b200 import config as gcfg
     gcfg.reload_flags()
     try:
         _, outs2, _ = run(use_graphs=False)
