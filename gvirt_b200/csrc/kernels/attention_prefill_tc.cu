@@ -21,7 +21,9 @@
 //     once, the softmax scale rides in the multiply-add that forms the exponent, and 2^x is the
 //     special-function instruction itself (`ex2.approx`);
 //   * two shapes (`Shape<BN>` below): 128-key tiles with one CTA per SM, or 64-key tiles with two
-//     CTAs per SM, where one CTA's MMAs and fixed parts overlap the other's softmax;
+//     CTAs per SM, where one CTA's MMAs and fixed parts overlap the other's softmax. (Giving a CTA
+//     two query tiles, the heaviest with the lightest, was measured too: it helps the one-CTA
+//     shape by 7 % and costs the two-CTA shape 7 % at 1024 tokens, so a CTA keeps one tile);
 //   * lazy rescaling: the running maximum only moves when a tile exceeds it by more than 2^8,
 //     so O is read back and scaled (tcgen05.ld / tcgen05.st) for a handful of tiles only.
 //

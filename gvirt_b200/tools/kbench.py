@@ -115,9 +115,12 @@ def case_attn(args):
     q = (torch.randn(B, nq * hd, device=dev) * 0.3).bfloat16()
     o = torch.empty_like(q)
     m.split_scratch = (torch.empty(B * nq * 32 * hd, device=dev), torch.empty(B * nq * 32, device=dev))
+    if args.variant >= 0:
+        # tile shape of the decode kernel: 1 / 2 / 3 = 16 tokens x 2 / 3 / 4 stages, 4 = 32 x 3, 0 = 32 x 2
+        _native.kernels().gv_set_decode_variant(args.variant)
     us = _time_us(lambda i: F.paged_attention(q, kcs[i % copies], vcs[i % copies], m, nq, nkv, hd, out=o), args)
     _report("attn_decode", us, B * ctx * nkv * hd * 2 * 2, args, batch=B, ctx=ctx, nq=nq, nkv=nkv,
-            splits=args.splits)
+            splits=args.splits, variant=args.variant)
 
 
 def case_mla(args):
@@ -422,6 +425,7 @@ def main() -> int:
     ap.add_argument("--nkv", type=int, default=8)
     ap.add_argument("--heads", type=int, default=128)
     ap.add_argument("--splits", type=int, default=1)
+    ap.add_argument("--variant", type=int, default=-1, help="attn: decode kernel tile shape (-1 = library default)")
     ap.add_argument("--tp", type=int, default=1)
     ap.add_argument("--chain", type=int, default=16)
     ap.add_argument("--reps", type=int, default=10)

@@ -519,10 +519,10 @@ def mode_tp_model_gpu(world):
         llm = LLM.from_config(cfg, ctx, seed=6, **llm_kw)
         seen = []
         orig = llm.model.compute_logits
-        llm.model.compute_logits = lambda hidden, meta, ws=None, batch=None: (
+        llm.model.compute_logits = lambda hidden, meta, ws=None, batch=None, **kw: (
             lambda lg: (seen.append(lg.detach().float().cpu())
                         if lg.device.type != "meta" and not torch.cuda.is_current_stream_capturing() else None, lg)[1])(
-                orig(hidden, meta, ws, batch))
+                orig(hidden, meta, ws, batch, **kw))
         return llm, [o.output for o in llm.generate(prompts, sp)], seen
 
     llm, outs, seen = run()
