@@ -18,6 +18,7 @@ from gvirt_b200.config import ModelConfig  # noqa: E402
 from gvirt_b200.engine.llm import LLM  # noqa: E402
 from gvirt_b200.engine.scheduler import SamplingParams  # noqa: E402
 from gvirt_b200.models import weights as W  # noqa: E402
+from gvirt_b200.ops import functional as F  # noqa: E402
 from gvirt_b200.parallel import collectives as coll  # noqa: E402
 from gvirt_b200.parallel import state as pstate  # noqa: E402
 from gvirt_b200.reference_cpu.oracle import NaiveDecoder  # noqa: E402
@@ -349,6 +350,28 @@ def mode_moe_ep_slice_cpu(world):
     want = oracle_tokens(kw, prompts, 5, 4)
     assert CollectiveExchange.calls > 0, "the sliced exchange path was not taken"
     assert [o.output for o in outs] == want, (ctx.rank, [o.output for o in outs], want)
+
+
+def mode_vocab_greedy_cpu(world):
+    """Greedy tokens picked per vocabulary shard (16 bytes per request gathered) equal argmax over the
+    gathered logits, also when the best score occurs in two shards (the lowest token id wins)."""
+    from gvirt_b200.models.transformer import Transformer
+    ctx = pstate.init_parallel(tp=world, dp=1, ep=1, backend="gloo", device="cpu")
+    cfg = tiny(tp_size=world)
+    w = W.init_random(cfg, ctx, seed=2, device="cpu")
+    model = Transformer(cfg, w, ctx)
+    g = torch.Generator().manual_seed(5)
+    B, H = 6, cfg.hidden_size
+    hidden = torch.randn(B, H, generator=g)
+    lm = w.lm_head if w.lm_head is not None else w.embed
+    # a tie across shards: every rank's local row 3 is the same vector, scaled to dominate
+    lm[3] = hidden[0] * 4.0
+    z = torch.zeros(1, dtype=torch.int32)
+    meta = F.AttnMeta(z, z, z, torch.arange(B, dtype=torch.int32), z, z.view(1, 1), z.long(), batch=B, num_tokens=B)
+    want = F.sample(model.compute_logits(hidden, meta, batch=B))
+    got = model.greedy_tokens(hidden, meta, batch=B)
+    assert torch.equal(want.to(torch.int32), got.to(torch.int32)), (ctx.rank, want, got)
+    assert int(got[0]) == 3, got          # the tie is won by the first shard's token
 
 
 def mode_dp_ep_cpu(world):

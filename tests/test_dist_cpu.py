@@ -32,7 +32,7 @@ def run_workers(mode, world=2, timeout=600, extra_env=None):
     return r.stdout
 
 
-@pytest.mark.parametrize("mode", ["collectives_cpu", "tp_cpu", "sp_cpu", "moe_ep_cpu", "moe_ep_slice_cpu", "dp_ep_cpu", "kv_transfer_cpu",
+@pytest.mark.parametrize("mode", ["collectives_cpu", "tp_cpu", "sp_cpu", "moe_ep_cpu", "moe_ep_slice_cpu", "vocab_greedy_cpu", "dp_ep_cpu", "kv_transfer_cpu",
                                   "dual_stream_cpu", "spec_tp_cpu", "serve_tp_cpu", "serve_dp_cpu", "serve_fail_cpu"])
 def test_two_ranks(mode):
     run_workers(mode, 2)
