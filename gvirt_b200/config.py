@@ -296,12 +296,13 @@ class EnvFlags:
     fuse_swiglu: bool = True             # GVIRT_FUSE_SWIGLU: SwiGLU in the gate/up GEMM epilogue
     decode_l2_prefetch: bool = False     # GVIRT_DECODE_L2_PREFETCH: a decode GEMM warms L2 with the next GEMM's first
                                          # tiles (measured: +3.6 us per Llama-3-8B layer at TP1, so off)
-    vocab_parallel_greedy: bool = False  # GVIRT_VOCAB_PARALLEL_GREEDY: all-greedy steps under TP pick the best
+    vocab_parallel_greedy: bool = True   # GVIRT_VOCAB_PARALLEL_GREEDY: all-greedy steps under TP pick the best
                                          # token per vocabulary shard and all-gather (score, id) pairs
                                          # instead of the logits
-    tp_pdl: bool = False                 # GVIRT_TP_PDL: keep programmatic dependent launch on under tensor
-                                         # parallelism (measured slower across GPUs: Llama-3-8B TP4 16.5 k
-                                         # tok/s with it, 21.5 k without)
+    tp_pdl: bool = False                 # GVIRT_TP_PDL: keep programmatic dependent launch on for dense models
+                                         # under tensor parallelism (measured slower across GPUs: Llama-3-8B
+                                         # TP4 16.5 k tok/s with it, 21.5 k without; MoE models keep it on:
+                                         # Qwen3-30B-A3B on 4 GPUs 14.9 k with, 14.4 k without)
     fused_ar_residual: bool = True       # GVIRT_FUSED_AR_RESIDUAL: under TP the fused GEMM + all-reduce also adds the
                                          # residual and emits the RMSNorm sums of squares (false: a small kernel behind it)
     prefill_attn_tc: bool = True         # GVIRT_PREFILL_ATTN_TC: tcgen05 flash attention for 128-wide heads

@@ -83,10 +83,11 @@ def attach_device_comm(ctx, cfg: ModelConfig) -> None:
     attach_symmetric_heap(ctx, nbytes=heap_bytes(cfg, ctx.tp) if ctx.tp > 1 else 0, ep_nbytes=ep_bytes)
     if getattr(ctx, "symm", None) is not None:
         ctx.symm.sp_rows_cap = sp_rows_per_rank(cfg, ctx.tp)
-    if ctx.tp > 1 and not flags().tp_pdl:
+    if ctx.tp > 1 and not flags().tp_pdl and not cfg.is_moe:
         # Across GPUs a kernel that starts before the one in front has drained shares SMs and HBM
-        # with the fused GEMM + all-reduce, whose push phase every peer waits for: measured, the
-        # early starts cost more there than they hide (they pay off on one GPU).
+        # with the fused GEMM + all-reduce, whose push phase every peer waits for: in the dense
+        # decode loop (two such kernels among five per layer) the early starts cost more than they
+        # hide. They still pay on one GPU and in MoE layers, whose many short kernels gain more.
         from .. import _native
         _native.kernels().gv_set_pdl(0)
     if use_a2a:
