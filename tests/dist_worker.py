@@ -548,7 +548,16 @@ def mode_tp_model_gpu(world):
                 orig(hidden, meta, ws, batch, **kw))
         return llm, [o.output for o in llm.generate(prompts, sp)], seen
 
-    llm, outs, seen = run()
+    # the first run assembles the full logits (compared with the oracle below); the second one picks
+    # the tokens per vocabulary shard, which is the default
+    from gvirt_b200 import config as gcfg
+    os.environ["GVIRT_VOCAB_PARALLEL_GREEDY"] = "0"
+    gcfg.reload_flags()
+    try:
+        llm, outs, seen = run()
+    finally:
+        os.environ.pop("GVIRT_VOCAB_PARALLEL_GREEDY", None)
+        gcfg.reload_flags()
     assert llm.model.fused_decode, "the fused decode loop is expected on this configuration"
     toks = torch.tensor(outs, device=ctx.device)
     gathered = [torch.empty_like(toks) for _ in range(world)]
@@ -568,9 +577,7 @@ def mode_tp_model_gpu(world):
     assert worst <= 0.06, f"first-step logits differ from the fp32 oracle by {worst:.3f} of the largest logit"
     # (2b) tokens picked per vocabulary shard (16 bytes per request gathered instead of the logits)
     # must be the tokens picked from the assembled logits
-    from gvirt_b200 import config as gcfg
-    before = gcfg.flags().vocab_parallel_greedy
-    os.environ["GVIRT_VOCAB_PARALLEL_GREEDY"] = "0" if before else "1"
+    os.environ["GVIRT_VOCAB_PARALLEL_GREEDY"] = "1"
     gcfg.reload_flags()
     try:
         _, outs_other, _ = run()
